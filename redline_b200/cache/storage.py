@@ -52,24 +52,31 @@ class StateStorage:
     than the manager hands out: index ``num_slots`` belongs to the padding rows of fixed-shape batches."""
 
     def __init__(self, specs: Dict[int, StateSpec], num_slots: int, device: torch.device):
-        self.pools: Dict[int, torch.Tensor] = {
-            call: torch.zeros((num_slots + 1,) + tuple(s.shape), dtype=getattr(torch, s.dtype), device=device)
-            for call, s in specs.items()
+        """``specs[call]`` is one ``StateSpec`` or a tuple of them (the call then gets a tuple of pools)."""
+        def pool(s: StateSpec) -> torch.Tensor:
+            return torch.zeros((num_slots + 1,) + tuple(s.shape), dtype=getattr(torch, s.dtype), device=device)
+
+        self.pools: Dict[int, object] = {
+            call: tuple(pool(x) for x in s) if isinstance(s, (tuple, list)) else pool(s) for call, s in specs.items()
         }
 
-    def snapshot(self) -> Dict[int, torch.Tensor]:
-        return {call: p.clone() for call, p in self.pools.items()}
+    def _all(self):
+        for p in self.pools.values():
+            yield from (p if isinstance(p, tuple) else (p,))
 
-    def restore(self, saved: Dict[int, torch.Tensor]) -> None:
-        for call, p in self.pools.items():
-            p.copy_(saved[call])
+    def snapshot(self) -> List[torch.Tensor]:
+        return [p.clone() for p in self._all()]
 
-    def of_call(self, call: int) -> Optional[torch.Tensor]:
+    def restore(self, saved: List[torch.Tensor]) -> None:
+        for p, old in zip(self._all(), saved):
+            p.copy_(old)
+
+    def of_call(self, call: int):
         return self.pools.get(call)
 
     def reset_slot(self, slot: int) -> None:
-        for p in self.pools.values():
+        for p in self._all():
             p[slot].zero_()
 
     def nbytes(self) -> int:
-        return sum(p.numel() * p.element_size() for p in self.pools.values())
+        return sum(p.numel() * p.element_size() for p in self._all())

@@ -539,3 +539,261 @@ class PufevikConfig(ModelConfig):
         if self.eos_token_ids:
             out["eos_token_id"] = list(self.eos_token_ids)
         return out
+
+
+# ------------------------------------------------------------------------------------ Vizotar
+
+@dataclass(frozen=True)
+class VizotarScaling:
+    """YaRN scaling of a rotation's frequencies."""
+
+    factor: float
+    original: int
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
+class VizotarRotation:
+    base: float
+    dims: int                 # the first so many entries of every head are rotated, entry i with i + dims / 2
+    scaling: Optional[VizotarScaling] = None
+
+
+@dataclass(frozen=True)
+class VizotarAttention:
+    """The left side of a 'parallel' mixer: windowed softmax attention with a sink."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    window: int               # mask.size; 0: every earlier key
+    conv: int                 # taps of the convolution behind q, k and v; 0: none
+    rot: Optional[VizotarRotation]
+
+
+@dataclass(frozen=True)
+class VizotarMemory:
+    heads: int
+    dim: int
+    vdim: int
+    gate_cap: float
+
+
+@dataclass(frozen=True)
+class VizotarParallel:
+    left: VizotarAttention
+    right: VizotarMemory
+
+
+@dataclass(frozen=True)
+class VizotarDelta:
+    """A 'channel_delta' mixer.  The inner sizes of its two low-rank projections are not in config.json: they are
+    the checkpoint's tensor shapes (``decay_rank`` / ``gate_rank`` may be given for a model without a file)."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    decay_rank: int
+    gate_rank: int
+
+
+@dataclass(frozen=True)
+class VizotarMLP:
+    kind: str                 # dense | moe
+    ff: int                   # dense: width of the layer; moe: of one expert
+    limit: float = 0.0        # dense: the clamp of gate and up
+    experts: int = 0
+    top: int = 0
+
+
+@dataclass(frozen=True)
+class VizotarLayer:
+    type: str                 # parallel | channel_delta
+    mixer: Any
+    mlp: Optional[VizotarMLP]
+    weights_of: Optional[int] = None     # the layer whose tensors this one uses (caches and states are its own)
+
+
+def _safetensors_shapes(model_dir: Optional[str]) -> Dict[str, Tuple[int, ...]]:
+    """Tensor name -> shape from the header of ``model.safetensors`` (empty if there is no such file)."""
+    if not model_dir:
+        return {}
+    path = os.path.join(model_dir, "model.safetensors")
+    try:
+        with open(path, "rb") as f:
+            n = int.from_bytes(f.read(8), "little")
+            if not 0 < n < (1 << 30):
+                return {}
+            header = json.loads(f.read(n))
+    except (OSError, ValueError):
+        return {}
+    return {k: tuple(v["shape"]) for k, v in header.items() if k != "__metadata__" and isinstance(v, dict)}
+
+
+@dataclass(frozen=True)
+class VizotarConfig(ModelConfig):
+    """``Vizotar``: pre-norm sublayers on ``streams`` residual streams (hyper-connections).  Mixers: a pair side by
+    side (windowed attention with a sink, short convolutions behind q, k and v, norms over the whole projection
+    and a partly rotated head with YaRN scaling, beside a matrix memory with exponential gates; each side's
+    output RMS-normed, then their mean), or the gated delta rule with a decay per key channel.  Feed-forwards:
+    dense with clamped gate and up, or routed experts (softmax over the chosen logits).  A layer may use
+    another layer's tensors.  The head is the embedding table.  config.json lists the layers under ``layers``."""
+
+    norm_eps: float = 1e-6
+    streams: int = 1
+    layers: Tuple[VizotarLayer, ...] = ()
+    raw: Optional[Dict[str, Any]] = field(default=None, compare=False, repr=False)
+
+    @staticmethod
+    def _attention(m: Dict[str, Any], where: str) -> VizotarAttention:
+        rot = m.get("rot")
+        r = None
+        if rot:
+            sc = rot.get("scaling")
+            w = where + ".rot.scaling"
+            r = VizotarRotation(float(_need(rot, "base", where + ".rot")), int(_need(rot, "dims", where + ".rot")),
+                                VizotarScaling(float(_need(sc, "factor", w)), int(_need(sc, "original", w)),
+                                               float(_need(sc, "fast", w)), float(_need(sc, "slow", w))) if sc else None)
+        heads = int(_need(m, "heads", where))
+        return VizotarAttention(heads=heads, kv_heads=int(m.get("kv_heads") or heads), dim=int(_need(m, "dim", where)),
+                                vdim=int(_need(m, "vdim", where)), scale=float(_need(m, "scale", where)),
+                                window=int((m.get("mask") or {}).get("size", 0)), conv=int(m.get("conv") or 0), rot=r)
+
+    @classmethod
+    def from_hf(cls, cfg: Dict[str, Any], model_dir: Optional[str] = None) -> "VizotarConfig":
+        shapes = _safetensors_shapes(model_dir)
+        entries = _need(cfg, "layers")
+        layers: List[VizotarLayer] = []
+        for i, entry in enumerate(entries):
+            where = f"layers[{i}]"
+            kind = _need(entry, "type", where)
+            m = _need(entry, "mixer", where)
+            src = entry.get("weights_of")
+            if src is not None and not (isinstance(src, int) and 0 <= src < i and entries[src].get("weights_of") is None):
+                raise ConfigError(f"{where}: weights_of must name an earlier layer that has tensors of its own")
+            if kind == "parallel":
+                r = _need(m, "right", where + ".mixer")
+                rw = where + ".mixer.right"
+                mixer: Any = VizotarParallel(
+                    left=cls._attention(_need(m, "left", where + ".mixer"), where + ".mixer.left"),
+                    right=VizotarMemory(int(_need(r, "heads", rw)), int(_need(r, "dim", rw)), int(_need(r, "vdim", rw)),
+                                        float(_need(r, "gate_cap", rw))))
+            elif kind == "channel_delta":
+                heads = int(_need(m, "heads", where + ".mixer"))
+                p = f"l{i if src is None else src}.mix."
+                ranks = []
+                for key, name in (("decay_rank", "a1"), ("gate_rank", "g1")):
+                    if p + name in shapes:
+                        ranks.append(int(shapes[p + name][0]))
+                    elif m.get(key) is not None:
+                        ranks.append(int(m[key]))
+                    else:
+                        raise ConfigError(f"{where}.mixer: the inner size of '{name}' is neither a tensor shape of the "
+                                          f"checkpoint nor given as '{key}'")
+                mixer = VizotarDelta(heads=heads, kv_heads=int(m.get("kv_heads") or heads),
+                                     dim=int(_need(m, "dim", where + ".mixer")), vdim=int(_need(m, "vdim", where + ".mixer")),
+                                     conv=int(_need(m, "conv", where + ".mixer")), decay_rank=ranks[0], gate_rank=ranks[1])
+            else:
+                raise ConfigError(f"{where}: mixer type '{kind}' is not supported (parallel, channel_delta)")
+            mlp = entry.get("mlp")
+            ff: Optional[VizotarMLP] = None
+            if mlp is not None:
+                mk = _need(mlp, "kind", where + ".mlp")
+                if mk == "dense":
+                    ff = VizotarMLP("dense", int(_need(mlp, "ff", where + ".mlp")), limit=float(_need(mlp, "limit", where + ".mlp")))
+                elif mk == "moe":
+                    r = _need(mlp, "router", where + ".mlp")
+                    ff = VizotarMLP("moe", int(_need(_need(mlp, "expert", where + ".mlp"), "ff", where + ".mlp.expert")),
+                                    experts=int(_need(r, "experts", where + ".mlp.router")),
+                                    top=int(_need(r, "top", where + ".mlp.router")))
+                else:
+                    raise ConfigError(f"{where}.mlp: kind '{mk}' is not supported (dense, moe)")
+            layers.append(VizotarLayer(kind, mixer, ff, src))
+        eos = cfg.get("eos_token_id")
+        eos = [] if eos is None else ([eos] if isinstance(eos, int) else list(eos))
+        bos = cfg.get("bos_token_id")
+        c = cls(architecture="Vizotar", vocab_size=int(_need(cfg, "vocab")), hidden_size=int(_need(cfg, "width")),
+                max_position_embeddings=int(cfg.get("max_positions", 1 << 30)),
+                bos_token_id=int(bos) if bos is not None else -1, eos_token_ids=tuple(int(e) for e in eos),
+                norm_eps=float(_need(_need(cfg, "norm"), "eps", "norm")), streams=int(cfg.get("streams", 1)),
+                layers=tuple(layers), raw=dict(cfg))
+        c.validate()
+        return c
+
+    def validate(self) -> None:
+        if self.vocab_size <= 0 or self.hidden_size <= 0 or not self.layers:
+            raise ConfigError("vocab, width and the number of layers must be positive")
+        if not self.norm_eps > 0:
+            raise ConfigError(f"norm.eps must be positive, got {self.norm_eps}")
+        if not 1 <= self.streams <= 8:
+            raise ConfigError(f"streams must lie between 1 and 8, got {self.streams}")
+        for i, layer in enumerate(self.layers):
+            m = layer.mixer
+            if layer.weights_of is not None and (self.layers[layer.weights_of].type != layer.type
+                                                 or self.layers[layer.weights_of].mixer != m
+                                                 or self.layers[layer.weights_of].mlp != layer.mlp):
+                raise ConfigError(f"layers[{i}]: a layer that uses another one's tensors has the same mixer and mlp entries")
+            if layer.type == "parallel":
+                a, r = m.left, m.right
+                if a.heads <= 0 or a.kv_heads <= 0 or a.heads % a.kv_heads != 0 or a.dim <= 0 or a.vdim <= 0:
+                    raise ConfigError(f"layers[{i}].mixer.left: heads must be a positive multiple of kv_heads, dim and vdim positive")
+                if a.rot is not None and (a.rot.dims <= 0 or a.rot.dims % 2 != 0 or a.rot.dims > a.dim):
+                    raise ConfigError(f"layers[{i}].mixer.left: rot.dims must be even and at most dim")
+                if a.rot is not None and a.rot.scaling is not None and not (
+                        a.rot.scaling.factor > 0 and a.rot.scaling.original > 0 and a.rot.scaling.fast > 0
+                        and a.rot.scaling.slow > 0 and a.rot.base > 1):
+                    raise ConfigError(f"layers[{i}].mixer.left: rot.scaling needs positive factor, original, fast and slow")
+                if a.window < 0 or not 0 <= a.conv <= 8:
+                    raise ConfigError(f"layers[{i}].mixer.left: mask.size must not be negative, conv at most 8")
+                if r.heads <= 0 or r.dim <= 0 or r.vdim <= 0 or not r.gate_cap > 0:
+                    raise ConfigError(f"layers[{i}].mixer.right: heads, dim, vdim and gate_cap must be positive")
+            else:
+                if m.heads <= 0 or m.kv_heads <= 0 or m.heads % m.kv_heads != 0 or m.dim <= 0 or m.vdim <= 0:
+                    raise ConfigError(f"layers[{i}].mixer: heads must be a positive multiple of kv_heads, dim and vdim positive")
+                if not 1 <= m.conv <= 8 or m.decay_rank <= 0 or m.gate_rank <= 0:
+                    raise ConfigError(f"layers[{i}].mixer: conv must lie between 1 and 8, the inner sizes be positive")
+            f = layer.mlp
+            if f is not None and (f.ff <= 0 or (f.kind == "dense" and not f.limit > 0)
+                                  or (f.kind == "moe" and not 1 <= f.top <= f.experts)):
+                raise ConfigError(f"layers[{i}].mlp: ff and limit must be positive, top between 1 and experts")
+
+    def to_hf(self) -> Dict[str, Any]:
+        layers = []
+        for layer in self.layers:
+            m = layer.mixer
+            if layer.type == "parallel":
+                a, r = m.left, m.right
+                left: Dict[str, Any] = {"heads": a.heads, "kv_heads": a.kv_heads, "dim": a.dim, "vdim": a.vdim,
+                                        "scale": a.scale, "mask": {"size": a.window}, "conv": a.conv}
+                if a.rot is not None:
+                    left["rot"] = {"base": a.rot.base, "dims": a.rot.dims}
+                    if a.rot.scaling is not None:
+                        s = a.rot.scaling
+                        left["rot"]["scaling"] = {"factor": s.factor, "original": s.original, "fast": s.fast, "slow": s.slow}
+                mixer = {"left": left, "right": {"heads": r.heads, "dim": r.dim, "vdim": r.vdim, "gate_cap": r.gate_cap}}
+            else:
+                mixer = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "conv": m.conv,
+                         "decay_rank": m.decay_rank, "gate_rank": m.gate_rank}
+            f = layer.mlp
+            if f is None:
+                mlp = None
+            elif f.kind == "dense":
+                mlp = {"kind": "dense", "ff": f.ff, "limit": f.limit}
+            else:
+                mlp = {"kind": "moe", "expert": {"ff": f.ff}, "router": {"experts": f.experts, "top": f.top}}
+            entry = {"type": layer.type, "mixer": mixer, "mlp": mlp}
+            if layer.weights_of is not None:
+                entry["weights_of"] = layer.weights_of
+            layers.append(entry)
+        out = {"architecture": "Vizotar", "vocab": self.vocab_size, "width": self.hidden_size, "streams": self.streams,
+               "norm": {"eps": self.norm_eps}, "layers": layers}
+        if self.bos_token_id >= 0:
+            out["bos_token_id"] = self.bos_token_id
+        if self.eos_token_ids:
+            out["eos_token_id"] = list(self.eos_token_ids)
+        return out

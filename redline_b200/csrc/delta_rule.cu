@@ -1,0 +1,276 @@
+// The gated delta rule: a matrix state per head that every token first decays row by row, then
+// corrects towards its value along its key, then reads with its query:
+//
+//     S <- diag(a_t) S            a_t one decay per key channel (row of S)
+//     d  = beta_t (v_t - S^T k_t)
+//     S <- S + k_t d^T
+//     o_t = S^T q_t                (the read-out sees the token's own write)
+//
+// S is [D, DV] per (request, head) in float32, in the request's state slot: zero for a new request,
+// carried from step to step.  Columns of S never mix, so a CTA owns 32 columns of one (sequence, head)
+// and walks the sequence's tokens in order; within a warp 8 columns x 4 groups of rows: a thread keeps
+// every fourth row of its column in registers and the two inner products are finished by two shuffles.
+// q, k and the decays of a few tokens at a time are staged in shared memory.  Everything here is float32:
+// q and k arrive as unit vectors, beta and the decays as numbers in (0, 1) (delta_prep_kernel makes them
+// from the projections); v is read in the activation type.
+//
+// delta_prep_kernel, one CTA per token: q and k heads (already convolved and activated) to unit vectors
+// x / sqrt(sum x^2 + floor), q times a constant; beta = sigmoid(z_b); a = exp(-exp(A_log_h) softplus(z_a + dt_bias)).
+// head_gated_norm_kernel, one warp per (token, head): o / sqrt(mean(o^2) + eps) * w * sigmoid(gate).
+//
+// RL_DELTA_DIM is the key size D (1..256), fixed when the file is compiled.
+#include "common.cuh"
+
+#ifndef RL_DELTA_DIM
+#define RL_DELTA_DIM 64
+#endif
+
+namespace rl {
+
+constexpr int kD = RL_DELTA_DIM;
+constexpr int kGroups = 4;                         // groups of rows a column is split into
+constexpr int kRows = (kD + kGroups - 1) / kGroups; // rows a thread keeps
+constexpr int kDP = kRows * kGroups;               // D rounded up; the rows beyond D stay zero
+constexpr int kCols = 32;                          // columns of a CTA (4 warps x 8)
+constexpr int kTok = 8;                            // tokens staged at a time
+
+// First token index t in [0, n) with seq_of_token[t] >= s (sequences lie in order in a step).
+__device__ __forceinline__ int first_token_of(const int32_t* __restrict__ seq_of_token, int n, int s) {
+  int lo = 0, hi = n;
+  while (lo < hi) {
+    const int mid = (lo + hi) >> 1;
+    if (seq_of_token[mid] < s) lo = mid + 1;
+    else hi = mid;
+  }
+  return lo;
+}
+
+template <typename T>
+struct DeltaArgs {
+  const float* q;          // [tokens, qk_heads * D] unit vectors, scaled
+  const float* k;          // [tokens, qk_heads * D] unit vectors
+  const T* v;              // [tokens, ld_v]: head h's values at h * DV
+  int ld_v;
+  const float* beta;       // [tokens, heads]
+  const float* decay;      // [tokens, heads * D]
+  const int32_t* seq_of_token;
+  const int32_t* state_slot;
+  float* state;            // [slots] x [heads, D, DV]
+  long long slot_stride;   // floats from one slot to the next
+  float* out;              // [tokens, heads * DV]
+  int tokens, heads, qk_heads, dv;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+delta_rule_kernel(const DeltaArgs<T> a) {
+  pdl_launch();
+  pdl_wait();
+  __shared__ float qs[kTok][kDP];
+  __shared__ float ks[kTok][kDP];
+  __shared__ float as[kTok][kDP];
+  __shared__ float vs[kTok][kCols];
+  __shared__ float bs[kTok];
+  const int seq = blockIdx.z, head = blockIdx.y;
+  const int qk_head = head / (a.heads / a.qk_heads);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int group = lane >> 3;                                   // rows group, group + 4, group + 8, ...
+  const int local_col = warp * 8 + (lane & 7);
+  const int col = blockIdx.x * kCols + local_col;
+  const bool mine = col < a.dv;
+  const int t0 = first_token_of(a.seq_of_token, a.tokens, seq);
+  const int t1 = first_token_of(a.seq_of_token, a.tokens, seq + 1);
+  if (t0 >= t1) return;
+  float* plane = a.state + static_cast<size_t>(a.state_slot[seq]) * a.slot_stride +
+                 static_cast<size_t>(head) * kD * a.dv;
+  float S[kRows];
+#pragma unroll
+  for (int i = 0; i < kRows; ++i) {
+    const int row = i * kGroups + group;
+    S[i] = (mine && row < kD) ? plane[static_cast<size_t>(row) * a.dv + col] : 0.f;
+  }
+  for (int tb = t0; tb < t1; tb += kTok) {
+    const int nt = min(kTok, t1 - tb);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * kDP; i += blockDim.x) {
+      const int tt = i / kDP, d = i - tt * kDP;
+      const size_t t = tb + tt;
+      const bool in = d < kD;
+      qs[tt][d] = in ? a.q[(t * a.qk_heads + qk_head) * kD + d] : 0.f;
+      ks[tt][d] = in ? a.k[(t * a.qk_heads + qk_head) * kD + d] : 0.f;
+      as[tt][d] = in ? a.decay[(t * a.heads + head) * kD + d] : 1.f;
+    }
+    for (int i = threadIdx.x; i < nt * kCols; i += blockDim.x) {
+      const int tt = i / kCols, c = i - tt * kCols;
+      const int gc = blockIdx.x * kCols + c;
+      vs[tt][c] = gc < a.dv ? to_float(a.v[static_cast<size_t>(tb + tt) * a.ld_v + head * a.dv + gc]) : 0.f;
+    }
+    if (threadIdx.x < nt) bs[threadIdx.x] = a.beta[static_cast<size_t>(tb + threadIdx.x) * a.heads + head];
+    __syncthreads();
+    for (int tt = 0; tt < nt; ++tt) {
+      float sk = 0.f;
+#pragma unroll
+      for (int i = 0; i < kRows; ++i) {
+        const int row = i * kGroups + group;
+        S[i] *= as[tt][row];
+        sk = fmaf(S[i], ks[tt][row], sk);
+      }
+      sk += __shfl_xor_sync(0xffffffffu, sk, 8);
+      sk += __shfl_xor_sync(0xffffffffu, sk, 16);
+      const float d = bs[tt] * (vs[tt][local_col] - sk);
+      float o = 0.f;
+#pragma unroll
+      for (int i = 0; i < kRows; ++i) {
+        const int row = i * kGroups + group;
+        S[i] = fmaf(ks[tt][row], d, S[i]);
+        o = fmaf(S[i], qs[tt][row], o);
+      }
+      o += __shfl_xor_sync(0xffffffffu, o, 8);
+      o += __shfl_xor_sync(0xffffffffu, o, 16);
+      if (mine && group == 0) a.out[(static_cast<size_t>(tb + tt) * a.heads + head) * a.dv + col] = o;
+    }
+  }
+  if (mine) {
+#pragma unroll
+    for (int i = 0; i < kRows; ++i) {
+      const int row = i * kGroups + group;
+      if (row < kD) plane[static_cast<size_t>(row) * a.dv + col] = S[i];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ what the recurrence is fed
+template <typename T>
+struct PrepArgs {
+  const T* x;              // [tokens, ld]: q heads at q_col, k heads at k_col (convolved, activated)
+  int ld, q_col, k_col, qk_heads, heads;
+  float q_scale, unit_floor;
+  const float* zb;         // [tokens, heads]       projection for beta
+  const float* za;         // [tokens, heads * D]   projection for the decays
+  const float* dt_bias;    // [heads * D]
+  const float* a_log;      // [heads]
+  float* q;                // [tokens, qk_heads * D]
+  float* k;
+  float* beta;             // [tokens, heads]
+  float* decay;            // [tokens, heads * D]
+};
+
+template <typename T>
+__global__ void delta_prep_kernel(const PrepArgs<T> a) {
+  pdl_launch();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const T* row = a.x + static_cast<size_t>(t) * a.ld;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+  for (int h = warp; h < 2 * a.qk_heads; h += nwarps) {       // a warp per head: first the q heads, then the k heads
+    const bool is_q = h < a.qk_heads;
+    const int hh = is_q ? h : h - a.qk_heads;
+    const T* p = row + (is_q ? a.q_col : a.k_col) + hh * kD;
+    float ss = 0.f;
+    for (int d = lane; d < kD; d += 32) {
+      const float v = to_float(p[d]);
+      ss = fmaf(v, v, ss);
+    }
+    ss = warp_sum(ss);
+    const float r = rsqrtf(ss + a.unit_floor) * (is_q ? a.q_scale : 1.f);
+    float* o = (is_q ? a.q : a.k) + (static_cast<size_t>(t) * a.qk_heads + hh) * kD;
+    for (int d = lane; d < kD; d += 32) o[d] = to_float(p[d]) * r;
+  }
+  for (int h = threadIdx.x; h < a.heads; h += blockDim.x)
+    a.beta[static_cast<size_t>(t) * a.heads + h] = 1.f / (1.f + expf(-a.zb[static_cast<size_t>(t) * a.heads + h]));
+  const int n = a.heads * kD;
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const float z = a.za[static_cast<size_t>(t) * n + i] + a.dt_bias[i];
+    const float sp = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
+    a.decay[static_cast<size_t>(t) * n + i] = expf(-expf(a.a_log[i / kD]) * sp);
+  }
+}
+
+// ------------------------------------------------------------------ per-head norm, weight and gate
+template <typename T, typename TW>
+__global__ void head_gated_norm_kernel(const float* __restrict__ o, const T* __restrict__ gate, int ld_gate,
+                                       const TW* __restrict__ w, int w_per_head, T* __restrict__ out, int ld_out,
+                                       int tokens, int heads, int dv, float eps) {
+  pdl_launch();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int item = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= tokens * heads) return;
+  const int t = item / heads, h = item - t * heads;
+  const float* p = o + (static_cast<size_t>(t) * heads + h) * dv;
+  float ss = 0.f;
+  for (int d = lane; d < dv; d += 32) ss = fmaf(p[d], p[d], ss);
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / static_cast<float>(dv) + eps);
+  for (int d = lane; d < dv; d += 32) {
+    float y = p[d] * r * to_float(w[w_per_head ? h * dv + d : d]);
+    if (gate != nullptr) y *= 1.f / (1.f + expf(-to_float(gate[static_cast<size_t>(t) * ld_gate + h * dv + d])));
+    out[static_cast<size_t>(t) * ld_out + h * dv + d] = from_float<T>(y);
+  }
+}
+
+}  // namespace rl
+
+using namespace rl;
+
+extern "C" {
+
+enum { RL_F32 = 0, RL_BF16 = 1 };
+
+int rl_delta_dim() { return kD; }
+
+int rl_delta_prep(int act_dtype, const void* x, int ld, int q_col, int k_col, int qk_heads, int heads, float q_scale,
+                  float unit_floor, const float* zb, const float* za, const float* dt_bias, const float* a_log,
+                  float* q, float* k, float* beta, float* decay, int tokens, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+#define RL_CASE(T)                                                                                               \
+  do {                                                                                                           \
+    PrepArgs<T> a;                                                                                               \
+    a.x = static_cast<const T*>(x); a.ld = ld; a.q_col = q_col; a.k_col = k_col; a.qk_heads = qk_heads;          \
+    a.heads = heads; a.q_scale = q_scale; a.unit_floor = unit_floor; a.zb = zb; a.za = za; a.dt_bias = dt_bias;  \
+    a.a_log = a_log; a.q = q; a.k = k; a.beta = beta; a.decay = decay;                                           \
+    launch_kernel(delta_prep_kernel<T>, dim3(tokens), dim3(256), 0, stream, a);                                  \
+  } while (0)
+  if (act_dtype == RL_F32) RL_CASE(float);
+  else RL_CASE(bf16);
+#undef RL_CASE
+  RL_LAUNCH_END();
+}
+
+int rl_delta_rule(int act_dtype, const float* q, const float* k, const void* v, int ld_v, const float* beta,
+                  const float* decay, const int32_t* seq_of_token, const int32_t* state_slot, float* state,
+                  long long slot_stride, float* out, int tokens, int sequences, int heads, int qk_heads, int dv,
+                  cudaStream_t stream) {
+  if (tokens <= 0 || sequences <= 0) return 0;
+  const dim3 grid((dv + kCols - 1) / kCols, heads, sequences);
+#define RL_CASE(T)                                                                                               \
+  do {                                                                                                           \
+    DeltaArgs<T> a;                                                                                              \
+    a.q = q; a.k = k; a.v = static_cast<const T*>(v); a.ld_v = ld_v; a.beta = beta; a.decay = decay;             \
+    a.seq_of_token = seq_of_token; a.state_slot = state_slot; a.state = state; a.slot_stride = slot_stride;      \
+    a.out = out; a.tokens = tokens; a.heads = heads; a.qk_heads = qk_heads; a.dv = dv;                           \
+    launch_kernel(delta_rule_kernel<T>, grid, dim3(128), 0, stream, a);                                          \
+  } while (0)
+  if (act_dtype == RL_F32) RL_CASE(float);
+  else RL_CASE(bf16);
+#undef RL_CASE
+  RL_LAUNCH_END();
+}
+
+int rl_head_gated_norm(int act_dtype, const float* o, const void* gate, int ld_gate, const void* w, int w_dtype,
+                       int w_per_head, void* out, int ld_out, int tokens, int heads, int dv, float eps,
+                       cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  const int warps = 8;
+  const dim3 grid((tokens * heads + warps - 1) / warps);
+#define RL_CASE(T, TW)                                                                                          \
+  launch_kernel(head_gated_norm_kernel<T, TW>, grid, dim3(warps * 32), 0, stream, o, static_cast<const T*>(gate), \
+                ld_gate, static_cast<const TW*>(w), w_per_head, static_cast<T*>(out), ld_out, tokens, heads, dv, eps)
+  if (act_dtype == RL_F32) RL_CASE(float, float);
+  else if (w_dtype == RL_F32) RL_CASE(bf16, float);
+  else RL_CASE(bf16, bf16);
+#undef RL_CASE
+  RL_LAUNCH_END();
+}
+
+}  // extern "C"

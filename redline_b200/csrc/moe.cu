@@ -54,7 +54,8 @@ __device__ __forceinline__ ArgMax warp_argmax(ArgMax a) {
 template <typename TA, typename TW>
 __global__ void moe_route_kernel(const TA* __restrict__ x, int ld, const TW* __restrict__ router, int tokens,
                                  int width, int experts, int groups, int keep, int group_top, int top, int softmax,
-                                 int renorm, int32_t* __restrict__ choice, float* __restrict__ weight) {
+                                 int renorm, const float* __restrict__ bias, int32_t* __restrict__ choice,
+                                 float* __restrict__ weight) {
   pdl_launch();
   pdl_wait();
   extern __shared__ float sm[];
@@ -79,6 +80,10 @@ __global__ void moe_route_kernel(const TA* __restrict__ x, int ld, const TW* __r
     }
   }
   __syncwarp();
+  if (bias != nullptr) {            // a bias of the router's logits
+    for (int e = lane; e < experts; e += 32) score[e] += bias[e];
+    __syncwarp();
+  }
   if (softmax) {
     float mx = -INFINITY;
     for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, score[e]);
@@ -500,8 +505,8 @@ extern "C" {
 int rl_moe_tile_rows() { return kTileRows; }
 
 int rl_moe_route(const void* x, int act_dtype, int ld, const void* router, int w_dtype, int tokens, int width,
-                 int experts, int groups, int keep, int group_top, int top, int softmax, int renorm, int32_t* choice,
-                 float* weight, cudaStream_t stream) {
+                 int experts, int groups, int keep, int group_top, int top, int softmax, int renorm, const float* bias,
+                 int32_t* choice, float* weight, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const int warps = 4;
   const size_t smem = static_cast<size_t>(warps) * (2 * experts + 2 * groups) * sizeof(float);
@@ -509,7 +514,7 @@ int rl_moe_route(const void* x, int act_dtype, int ld, const void* router, int w
 #define RL_CASE(TA, TW)                                                                                            \
   launch_kernel(moe_route_kernel<TA, TW>, grid, block, smem, stream, static_cast<const TA*>(x), ld,                \
                 static_cast<const TW*>(router), tokens, width, experts, groups, keep, group_top, top, softmax,     \
-                renorm, choice, weight)
+                renorm, bias, choice, weight)
   if (act_dtype == 0) RL_CASE(float, float);
   else if (w_dtype == 0) RL_CASE(bf16, float);
   else RL_CASE(bf16, bf16);

@@ -3,8 +3,8 @@
 // activation over a range of columns; the write of any per-token tensor into its paged cache; the
 // gated unit-RMS norm that closes a linear-attention mixer; a gated activation act(gate) * up; and what
 // attention heads may need between their projection and the cache: an RMS norm of queries and keys
-// (per head or over the whole projection), a rotation of neighbouring pairs, a mix of the values with
-// those of an earlier layer.
+// (per head or over the whole projection), a rotation of pairs (neighbours, or entry i with entry
+// i + half), a mix of the values with those of an earlier layer.
 //
 // Activations are float or bfloat16; means, variances, the stream and the activations'
 // arithmetic are float.  The variance is the mean of squared deviations (two passes over a row
@@ -13,7 +13,8 @@
 
 namespace rl {
 
-enum { ACT_NONE = 0, ACT_RELU_SQ = 1, ACT_GELU_ERF = 2, ACT_SILU = 3, ACT_GELU_TANH = 4, ACT_SIGMOID = 5 };
+enum { ACT_NONE = 0, ACT_RELU_SQ = 1, ACT_GELU_ERF = 2, ACT_SILU = 3, ACT_GELU_TANH = 4, ACT_SIGMOID = 5,
+       ACT_CLAMPED_SWISH = 6 };
 
 __device__ __forceinline__ float activate(float z, int mode) {
   switch (mode) {
@@ -250,14 +251,23 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const TA* __re
 }
 
 // ------------------------------------------------ out[r, i] = act(gu[r, i]) * gu[r, inter + i]
+// mode ACT_CLAMPED_SWISH: g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(slope g) (u + 1).
 template <typename TA>
-__global__ void gated_act_kernel(const TA* __restrict__ gu, int ld, TA* __restrict__ out, int inter, int mode) {
+__global__ void gated_act_kernel(const TA* __restrict__ gu, int ld, TA* __restrict__ out, int inter, int mode,
+                                 float limit, float slope) {
   pdl_launch();
   pdl_wait();
   const TA* g = gu + static_cast<size_t>(blockIdx.y) * ld;
   TA* o = out + static_cast<size_t>(blockIdx.y) * inter;
-  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < inter; c += gridDim.x * blockDim.x)
-    o[c] = from_float<TA>(activate(to_float(g[c]), mode) * to_float(g[inter + c]));
+  for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < inter; c += gridDim.x * blockDim.x) {
+    if (mode == ACT_CLAMPED_SWISH) {
+      const float z = fminf(to_float(g[c]), limit);
+      const float u = fminf(fmaxf(to_float(g[inter + c]), -limit), limit);
+      o[c] = from_float<TA>(z / (1.f + expf(-slope * z)) * (u + 1.f));
+    } else {
+      o[c] = from_float<TA>(activate(to_float(g[c]), mode) * to_float(g[inter + c]));
+    }
+  }
 }
 
 // ------------------------------------------------ queries, keys and values between projection and cache
@@ -266,7 +276,8 @@ __global__ void gated_act_kernel(const TA* __restrict__ gu, int ld, TA* __restri
 //   normed:   x / sqrt(mean(x^2) + eps) * w, the mean over one head (norm_mode 1, w of `dim` entries for all
 //             heads) or over the whole section (norm_mode 2, w of heads * dim entries); 0: not normed;
 //   rotated:  entries (2i, 2i+1), i < rot_pairs, of every head turn by the angle whose cosine and sine are
-//             cos[pos, i] and sin[pos, i] (tables [max_pos, rot_pairs]); the other entries stay.
+//             cos[pos, i] and sin[pos, i] (tables [max_pos, rot_pairs]); the other entries stay.  With rot_half
+//             the pairs are (i, i + rot_pairs) instead.
 // The values (v_size entries at v_col) are, with vmix_mode 1, copied to v_first [tokens, v_size]; with
 // vmix_mode 2 replaced by (1 - lam) v + lam v_first.  A position beyond the tables sets bit 1 of *status.
 // With `slots` the finished keys and values also go to their paged caches ([pages, k_heads, page_size, dim]
@@ -297,6 +308,7 @@ struct HeadPrepArgs {
   int v_heads, page_size;
   long long num_slots;
   int pairs_ok;       // every head starts on a pair's boundary in the buffer, the weights and the caches
+  int rot_half;       // 1: entry i < rot_pairs is paired with entry i + rot_pairs instead of its neighbour
 };
 
 template <typename TA, typename TW>
@@ -383,7 +395,9 @@ __global__ void head_prep_kernel(TA* __restrict__ x, const int32_t* __restrict__
     for (int i = threadIdx.x; i < n; i += blockDim.x) {
       const int h = i / a.dim, d = i - h * a.dim;
       const bool paired = d < 2 * a.rot_pairs;
-      if (paired && (d & 1)) continue;            // the odd entry of a pair goes with the even one
+      // the second entry of a pair goes with the first one
+      if (paired && (a.rot_half ? d >= a.rot_pairs : (d & 1))) continue;
+      const int other = a.rot_half ? a.rot_pairs : 1, pair = a.rot_half ? d : (d >> 1);
       const float r = a.norm_mode == 2 ? whole
                       : (a.norm_mode == 1 ? rsqrtf(head_sq[h0 + h] / static_cast<float>(a.dim) + a.eps) : 1.f);
       const int wi = a.norm_mode == 2 ? i : d;
@@ -396,16 +410,16 @@ __global__ void head_prep_kernel(TA* __restrict__ x, const int32_t* __restrict__
         if (c != nullptr) c[0] = o;
         continue;
       }
-      float v = to_float(p[i + 1]) * r;
-      if (a.norm_mode != 0) v *= to_float(w[wi + 1]);
-      const float cs = cos_t[static_cast<size_t>(pos) * a.rot_pairs + (d >> 1)];
-      const float sn = sin_t[static_cast<size_t>(pos) * a.rot_pairs + (d >> 1)];
+      float v = to_float(p[i + other]) * r;
+      if (a.norm_mode != 0) v *= to_float(w[wi + other]);
+      const float cs = cos_t[static_cast<size_t>(pos) * a.rot_pairs + pair];
+      const float sn = sin_t[static_cast<size_t>(pos) * a.rot_pairs + pair];
       const TA o0 = from_float<TA>(u * cs - v * sn), o1 = from_float<TA>(v * cs + u * sn);
       p[i] = o0;
-      p[i + 1] = o1;
+      p[i + other] = o1;
       if (c != nullptr) {
         c[0] = o0;
-        c[1] = o1;
+        c[other] = o1;
       }
     }
   }
@@ -512,17 +526,17 @@ int rl_gated_rmsnorm(const float* o, const void* gate, int ld_gate, const void* 
   RL_LAUNCH_END();
 }
 
-int rl_gated_act(const void* gu, int ld, void* out, int act_dtype, int rows, int inter, int mode,
-                 cudaStream_t stream) {
+int rl_gated_act(const void* gu, int ld, void* out, int act_dtype, int rows, int inter, int mode, float limit,
+                 float slope, cudaStream_t stream) {
   if (rows <= 0 || inter <= 0) return 0;
   const int th = 256;
   dim3 grid(min((inter + th - 1) / th, 64), rows);
   if (act_dtype == RL_F32)
     launch_kernel(gated_act_kernel<float>, grid, dim3(th), 0, stream, static_cast<const float*>(gu), ld,
-                  static_cast<float*>(out), inter, mode);
+                  static_cast<float*>(out), inter, mode, limit, slope);
   else
     launch_kernel(gated_act_kernel<bf16>, grid, dim3(th), 0, stream, static_cast<const bf16*>(gu), ld,
-                  static_cast<bf16*>(out), inter, mode);
+                  static_cast<bf16*>(out), inter, mode, limit, slope);
   RL_LAUNCH_END();
 }
 
@@ -530,15 +544,17 @@ int rl_head_prep(void* x, int act_dtype, int ld, const int32_t* positions, int t
                  int k_col, int k_heads, int dim, const void* q_w, const void* k_w, int w_dtype, int norm_mode,
                  float eps, const float* cos_t, const float* sin_t, int rot_pairs, int max_pos, int v_col,
                  int v_size, void* v_first, int vmix_mode, float lam, const int32_t* slots, void* k_cache,
-                 void* v_cache, int v_heads, int page_size, long long num_slots, int* status, cudaStream_t stream) {
+                 void* v_cache, int v_heads, int page_size, long long num_slots, int* status, int rot_half,
+                 cudaStream_t stream) {
   if (tokens <= 0) return 0;
   HeadPrepArgs a;
+  a.rot_half = rot_half;
   a.ld = ld; a.q_col = q_col; a.q_heads = q_heads; a.k_col = k_col; a.k_heads = k_heads; a.dim = dim;
   a.norm_mode = norm_mode; a.eps = eps; a.rot_pairs = rot_pairs; a.max_pos = max_pos; a.v_col = v_col;
   a.v_size = v_size; a.vmix_mode = vmix_mode; a.lam = lam;
   a.slots = slots; a.v_heads = v_heads; a.page_size = page_size; a.num_slots = num_slots;
   const size_t pair = act_dtype == RL_F32 ? 8 : 4, wpair = (act_dtype == RL_F32 || w_dtype == RL_F32) ? 8 : 4;
-  a.pairs_ok = dim % 2 == 0 && ld % 2 == 0 && q_col % 2 == 0 && k_col % 2 == 0 &&
+  a.pairs_ok = !(rot_half && rot_pairs > 0) && dim % 2 == 0 && ld % 2 == 0 && q_col % 2 == 0 && k_col % 2 == 0 &&
                reinterpret_cast<uintptr_t>(x) % pair == 0 && reinterpret_cast<uintptr_t>(k_cache) % pair == 0 &&
                reinterpret_cast<uintptr_t>(q_w) % wpair == 0 && reinterpret_cast<uintptr_t>(k_w) % wpair == 0;
   const int widest = max(q_heads, k_heads) * dim;

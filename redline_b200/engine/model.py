@@ -43,6 +43,16 @@ class DecoderModel:
                     raise ValueError("a layer with output norms has one for every sublayer")
                 block.mixer_post_norm = build_part("norm", ls.mixer_post_norm, rt)
                 block.ffn_post_norm = build_part("norm", ls.ffn_post_norm, rt) if ls.ffn_post_norm is not None else None
+            if ls.mixer_conn is not None or ls.ffn_conn is not None:
+                block = self.blocks[-1]
+                if not getattr(block_cls, "keeps_streams", False):
+                    raise ValueError(f"the block arrangement '{ls.arrangement}' keeps one residual stream")
+                if ls.mixer_conn is None or (ls.ffn is not None) != (ls.ffn_conn is not None):
+                    raise ValueError("a layer with several streams has a connection for every sublayer")
+                block.mixer_conn = build_part("connection", ls.mixer_conn, rt)
+                block.ffn_conn = build_part("connection", ls.ffn_conn, rt) if ls.ffn_conn is not None else None
+            elif getattr(block_cls, "keeps_streams", False):
+                raise ValueError(f"the block arrangement '{ls.arrangement}' needs its sublayers' connections")
         self.final_norm = build_part("norm", spec.final_norm, rt)
         self.head = build_part("head", spec.head, rt)
         self.nvtx_layers = False           # one NVTX range per layer call (set by the runner from the engine's options)

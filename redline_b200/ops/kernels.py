@@ -570,6 +570,7 @@ def attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: t
 # ------------------------------------------- row-wise kernels of blocks with norms on both sides
 
 ACT_NONE, ACT_RELU_SQ, ACT_GELU_ERF, ACT_SILU, ACT_GELU_TANH, ACT_SIGMOID = 0, 1, 2, 3, 4, 5
+ACT_CLAMPED_SWISH = 6      # gated_act only: min / clamp of gate and up, g * sigmoid(slope * g) * (up + 1)
 ACTIVATIONS = {"none": ACT_NONE, "relu_squared": ACT_RELU_SQ, "gelu": ACT_GELU_ERF, "silu": ACT_SILU,
                "gelu_tanh": ACT_GELU_TANH}
 NORM_LAYER, NORM_RMS = 0, 1
@@ -649,15 +650,16 @@ def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out
              rows if rows is not None else o.shape[0], o.shape[1], float(eps), _stream()), "gated_rmsnorm")
 
 
-def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: int) -> None:
-    """out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i], I = out.shape[1]."""
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: int, limit: float = 0.0, slope: float = 1.0) -> None:
+    """out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i], I = out.shape[1].  ``ACT_CLAMPED_SWISH``: with
+    g = min(gate, limit) and u = clamp(up, -limit, limit), out = g * sigmoid(slope * g) * (u + 1)."""
     _need_cuda(gate_up, out)
     if gate_up.stride(1) != 1 or not out.is_contiguous() or gate_up.dtype != out.dtype \
             or gate_up.shape[1] != 2 * out.shape[1]:
         raise KernelError("gated_act: [gate | up] rows of the output's type and twice its width")
-    f = _fn(_rw(), "rl_gated_act", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p])
+    f = _fn(_rw(), "rl_gated_act", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
     _check(f(_ptr(gate_up), gate_up.stride(0), _ptr(out), _code(out.dtype), out.shape[0], out.shape[1], act,
-             _stream()), "gated_act")
+             float(limit), float(slope), _stream()), "gated_act")
 
 
 HEAD_NORM_NONE, HEAD_NORM_EACH, HEAD_NORM_WHOLE = 0, 1, 2
@@ -670,11 +672,11 @@ def head_prep(x: torch.Tensor, positions: torch.Tensor, tokens: int, q_col: int,
               cos: Optional[torch.Tensor] = None, sin: Optional[torch.Tensor] = None, v_col: int = 0, v_size: int = 0,
               v_first: Optional[torch.Tensor] = None, mix_mode: int = VALUE_MIX_NONE, lam: float = 0.0,
               slots: Optional[torch.Tensor] = None, k_cache: Optional[torch.Tensor] = None,
-              v_cache: Optional[torch.Tensor] = None, page_size: int = 0) -> None:
+              v_cache: Optional[torch.Tensor] = None, page_size: int = 0, halves: bool = False) -> None:
     """In place on the rows of a projection buffer (csrc/rowwise.cu: head_prep_kernel): the query heads at
     ``q_col`` and the key heads at ``k_col`` are RMS-normed (per head with weights [dim], or over the whole
     section with weights [heads * dim]) and their first 2 * cos.shape[1] entries rotated in neighbouring
-    pairs by the tables' angles at each token's position; the values at ``v_col`` are kept in ``v_first``
+    pairs (``halves``: entry i paired with entry i + cos.shape[1]) by the tables' angles at each token's position; the values at ``v_col`` are kept in ``v_first``
     [tokens, v_size] or blended with it, v <- (1 - lam) v + lam v_first.  All in float32.  With ``slots`` the
     finished keys and values are also written to their paged caches ([pages, k_heads, page_size, dim] and
     [pages, v_heads, page_size, vdim]; a slot beyond the pool is not written and sets bit 2 of ``status``)."""
@@ -706,12 +708,12 @@ def head_prep(x: torch.Tensor, positions: torch.Tensor, tokens: int, q_col: int,
     f = _fn(_rw(), "rl_head_prep", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                                      c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p, c_int, c_int,
                                      c_int, c_int, c_void_p, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int,
-                                     c_int, c_longlong, c_void_p, c_void_p])
+                                     c_int, c_longlong, c_void_p, c_int, c_void_p])
     _check(f(_ptr(x), _code(x.dtype), x.stride(0), _ptr(positions), tokens, q_col, q_heads, k_col, k_heads, dim,
              _ptr(q_weight), _ptr(k_weight), _code(q_weight.dtype) if q_weight is not None else 0, norm_mode,
              float(eps), _ptr(cos), _ptr(sin), pairs, cos.shape[0] if cos is not None else 0, v_col, v_size,
              _ptr(v_first), mix_mode, float(lam), _ptr(slots), _ptr(k_cache), _ptr(v_cache), v_heads, page_size,
-             num_slots, _ptr(status), _stream()), "head_prep")
+             num_slots, _ptr(status), 1 if halves else 0, _stream()), "head_prep")
 
 
 # ------------------------------------ attention with score maps, a capped score and kept first tokens
@@ -898,6 +900,154 @@ def matrix_memory_output(num: torch.Tensor, qn: torch.Tensor, stab: torch.Tensor
              float(floor), float(out_scale), _stream()), "matrix_memory_output")
 
 
+# ------------------------------------------- several residual streams, normed pairs, short convolutions
+
+MAX_STREAMS = 8
+MAX_CONV_TAPS = 8
+
+
+def _so() -> ctypes.CDLL:
+    return _lib("stream_ops", "stream_ops.cu")
+
+
+def streams_step(streams: torch.Tensor, tokens: int, init: Optional[torch.Tensor] = None,
+                 y: Optional[torch.Tensor] = None, mix: Optional[torch.Tensor] = None,
+                 out_w: Optional[torch.Tensor] = None, read_in: Optional[torch.Tensor] = None,
+                 norm_w: Optional[torch.Tensor] = None, eps: float = 0.0, normed: Optional[torch.Tensor] = None,
+                 total: Optional[torch.Tensor] = None) -> None:
+    """One sublayer's boundary on the float32 streams [tokens, n, width] (csrc/stream_ops.cu): with ``init``
+    [tokens, width] every stream becomes a copy of it; with ``y`` (the sublayer's output, activation type) the
+    streams are mixed, X_t <- sum_s mix[s, t] X_s + out_w[t] y; with ``read_in`` the next sublayer's input is
+    formed, normed = rmsnorm(sum_s read_in[s] X_s) * norm_w; with ``total`` the sum of the streams is written.
+    mix, out_w and read_in are float32."""
+    _need_cuda(streams, init, y, mix, out_w, read_in, norm_w, normed, total)
+    n, width = streams.shape[1], streams.shape[2]
+    if streams.dtype != torch.float32 or not streams.is_contiguous() or not 1 <= n <= MAX_STREAMS:
+        raise KernelError(f"streams_step: contiguous float32 [tokens, n <= {MAX_STREAMS}, width]")
+    for t in (init, total):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous() or t.shape[1] != width):
+            raise KernelError("streams_step: init and total are contiguous float32 [tokens, width]")
+    if y is not None and (mix is None or out_w is None or mix.numel() != n * n or out_w.numel() != n
+                          or mix.dtype != torch.float32 or out_w.dtype != torch.float32 or y.stride(1) != 1):
+        raise KernelError("streams_step: a sublayer's output comes with float32 mix [n, n] and out [n]")
+    if read_in is not None and (norm_w is None or normed is None or read_in.numel() != n
+                                or read_in.dtype != torch.float32 or normed.stride(1) != 1
+                                or (y is not None and y.dtype != normed.dtype)):
+        raise KernelError("streams_step: read_in float32 [n] comes with a norm weight and a buffer for the normed rows")
+    act = normed if normed is not None else y
+    f = _fn(_so(), "rl_streams_step", [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_ptr(streams), _ptr(init), _ptr(y), y.stride(0) if y is not None else 0,
+             _ptr(mix.contiguous()) if mix is not None else None, _ptr(out_w), _ptr(read_in), _ptr(norm_w),
+             _code(norm_w.dtype) if norm_w is not None else 0, _ptr(normed),
+             normed.stride(0) if normed is not None else 0, _code(act.dtype) if act is not None else 0, _ptr(total),
+             tokens, n, width, float(eps), _stream()), "streams_step")
+
+
+def pair_norm_mean(a: torch.Tensor, wa: torch.Tensor, ca: float, b: torch.Tensor, wb: torch.Tensor, cb: float,
+                   out: torch.Tensor, eps: float, rows: Optional[int] = None) -> None:
+    """out = ca * rmsnorm(a) * wa + cb * rmsnorm(b) * wb over rows of the activation type (csrc/stream_ops.cu)."""
+    _need_cuda(a, b, wa, wb, out)
+    if a.dtype != b.dtype or a.dtype != out.dtype or wa.dtype != wb.dtype or a.shape[1] != b.shape[1] \
+            or a.stride(1) != 1 or b.stride(1) != 1 or out.stride(1) != 1 or wa.numel() != a.shape[1]:
+        raise KernelError("pair_norm_mean: two inputs and an output of one type and width, weights of one type")
+    f = _fn(_so(), "rl_pair_norm_mean", [c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_float,
+                                         c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_code(a.dtype), _ptr(a), a.stride(0), _ptr(wa), float(ca), _ptr(b), b.stride(0), _ptr(wb), float(cb),
+             _code(wa.dtype), _ptr(out), out.stride(0), rows if rows is not None else a.shape[0], a.shape[1],
+             float(eps), _stream()), "pair_norm_mean")
+
+
+def short_conv(x: torch.Tensor, col_x: int, w: torch.Tensor, bias: Optional[torch.Tensor], y: torch.Tensor, col_y: int,
+               act: int, seq_of_token: torch.Tensor, state_slot: torch.Tensor, state: torch.Tensor, tokens: int) -> None:
+    """Causal convolution over time on ``w.shape[0]`` channels of x's rows, from column ``col_x``, into y's from
+    ``col_y`` (another buffer): y_t = act(sum_j w[c, j] (x_(t - taps + 1 + j) + bias_c)) within a token's own
+    sequence; what lies before the step's portion comes from the sequence's slot of ``state`` (float32
+    [slots, (taps - 1) * channels]: the last inputs, zeros for a new request), which is then moved on
+    (csrc/stream_ops.cu).  ``act``: ACT_NONE or ACT_SILU."""
+    _need_cuda(x, w, bias, y, state)
+    channels, taps = w.shape
+    if x.dtype != y.dtype or x.stride(1) != 1 or y.stride(1) != 1 or not w.is_contiguous() \
+            or x.data_ptr() == y.data_ptr() or not 1 <= taps <= MAX_CONV_TAPS or act not in (ACT_NONE, ACT_SILU):
+        raise KernelError(f"short_conv: two buffers of one type, contiguous weights [channels, taps <= {MAX_CONV_TAPS}]")
+    if state.dtype != torch.float32 or state.stride(1) != 1 or state.shape[1] < (taps - 1) * channels:
+        raise KernelError("short_conv: the state is float32 [slots, (taps - 1) * channels]")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != channels or not bias.is_contiguous()):
+        raise KernelError("short_conv: the bias is contiguous float32 [channels]")
+    f = _fn(_so(), "rl_short_conv", [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                     c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p])
+    _check(f(_code(x.dtype), _ptr(x), x.stride(0), col_x, _ptr(w), _code(w.dtype), _ptr(bias), _ptr(y), y.stride(0),
+             col_y, channels, taps, act, _ptr(seq_of_token), _ptr(state_slot), _ptr(state), state.stride(0), tokens,
+             _stream()), "short_conv", 2 if taps > 1 else 1)
+
+
+# ------------------------------------------------------------------- the gated delta rule
+
+def _delta(dim: int) -> ctypes.CDLL:
+    if not 1 <= dim <= 256:
+        raise KernelError(f"delta_rule takes key sizes up to 256; got {dim}")
+    return _lib(f"delta_rule_d{dim}", "delta_rule.cu", {"RL_DELTA_DIM": dim})
+
+
+def delta_prep(x: torch.Tensor, q_col: int, k_col: int, qk_heads: int, heads: int, dim: int, q_scale: float,
+               unit_floor: float, zb: torch.Tensor, za: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor,
+               q: torch.Tensor, k: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor, tokens: int) -> None:
+    """What the delta rule's recurrence is fed (csrc/delta_rule.cu), all float32: q and k heads of x's rows as
+    unit vectors x / sqrt(sum x^2 + unit_floor) (q times ``q_scale``), beta = sigmoid(zb) per head, and per head
+    and key channel decay = exp(-exp(a_log_h) * softplus(za + dt_bias))."""
+    _need_cuda(x, zb, za, dt_bias, a_log, q, k, beta, decay)
+    for t in (zb, za, dt_bias, a_log, q, k, beta, decay):
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise KernelError("delta_prep: projections, constants and outputs are contiguous float32")
+    if x.stride(1) != 1 or zb.shape[1] != heads or za.shape[1] != heads * dim or dt_bias.numel() != heads * dim \
+            or a_log.numel() != heads or q.shape[1] != qk_heads * dim or heads % qk_heads != 0:
+        raise KernelError("delta_prep: bad shapes")
+    f = _fn(_delta(dim), "rl_delta_prep", [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float,
+                                           c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_int, c_void_p])
+    _check(f(_code(x.dtype), _ptr(x), x.stride(0), q_col, k_col, qk_heads, heads, float(q_scale), float(unit_floor),
+             _ptr(zb), _ptr(za), _ptr(dt_bias), _ptr(a_log), _ptr(q), _ptr(k), _ptr(beta), _ptr(decay), tokens,
+             _stream()), "delta_prep")
+
+
+def delta_rule(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, beta: torch.Tensor, decay: torch.Tensor,
+               seq_of_token: torch.Tensor, state_slot: torch.Tensor, state: torch.Tensor, out: torch.Tensor,
+               tokens: int, sequences: int, heads: int, qk_heads: int, dim: int, vdim: int) -> None:
+    """Per head S <- diag(decay) S; d = beta (v - S^T k); S <- S + k d^T; o = S^T q over every sequence of the
+    step, from and into the sequences' state slots (csrc/delta_rule.cu).  q, k float32 [tokens, qk_heads * dim],
+    v a row-strided view [tokens, heads * vdim] of the activation type, beta [tokens, heads], decay
+    [tokens, heads * dim], state float32 [slots, heads * dim * vdim], out float32 [tokens, heads * vdim]."""
+    _need_cuda(q, k, v, beta, decay, state, out)
+    for t in (q, k, beta, decay, out):
+        if t.dtype != torch.float32 or not t.is_contiguous():
+            raise KernelError("delta_rule: q, k, beta, decay and out are contiguous float32")
+    if state.dtype != torch.float32 or state.stride(1) != 1 or state.shape[1] < heads * dim * vdim or v.stride(1) != 1 \
+            or v.shape[1] != heads * vdim or heads % qk_heads != 0:
+        raise KernelError("delta_rule: bad shapes")
+    f = _fn(_delta(dim), "rl_delta_rule", [c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_void_p, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                           c_void_p])
+    _check(f(_code(v.dtype), _ptr(q), _ptr(k), _ptr(v), v.stride(0), _ptr(beta), _ptr(decay), _ptr(seq_of_token),
+             _ptr(state_slot), _ptr(state), state.stride(0), _ptr(out), tokens, sequences, heads, qk_heads, vdim,
+             _stream()), "delta_rule")
+
+
+def head_gated_norm(o: torch.Tensor, gate: Optional[torch.Tensor], weight: torch.Tensor, out: torch.Tensor,
+                    tokens: int, heads: int, vdim: int, eps: float, dim: int = 64) -> None:
+    """out = o / sqrt(mean over a head (o^2) + eps) * weight * sigmoid(gate): o float32 [tokens, heads * vdim],
+    weight [vdim] (one for all heads) or [heads * vdim], gate and out row-strided views of the activation type."""
+    _need_cuda(o, gate, weight, out)
+    if o.dtype != torch.float32 or not o.is_contiguous() or out.stride(1) != 1 \
+            or (gate is not None and (gate.stride(1) != 1 or gate.dtype != out.dtype)) \
+            or weight.numel() not in (vdim, heads * vdim):
+        raise KernelError("head_gated_norm: bad shapes")
+    f = _fn(_delta(dim), "rl_head_gated_norm", [c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p,
+                                                c_int, c_int, c_int, c_int, c_float, c_void_p])
+    _check(f(_code(out.dtype), _ptr(o), _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(weight),
+             _code(weight.dtype), 1 if weight.numel() == heads * vdim and heads > 1 else 0, _ptr(out), out.stride(0),
+             tokens, heads, vdim, float(eps), _stream()), "head_gated_norm")
+
+
 # ------------------------------------------------------------------- routed feed-forward
 
 def _moe() -> ctypes.CDLL:
@@ -913,12 +1063,16 @@ def moe_max_tiles(pairs: int, experts: int) -> int:
 
 
 def moe_route(x: torch.Tensor, router: Optional[torch.Tensor], choice: torch.Tensor, weight: torch.Tensor, tokens: int,
-              groups: int, keep: int, group_top: int, top: int, softmax: bool = False, renorm: bool = False) -> None:
+              groups: int, keep: int, group_top: int, top: int, softmax: bool = False, renorm: bool = False,
+              bias: Optional[torch.Tensor] = None) -> None:
     """Per token: scores of the experts (float32 sums; sigmoid, or softmax), the best ``keep`` of ``groups``
     groups of neighbouring experts by the sum of their ``group_top`` best scores, the ``top`` best experts
     of those into choice [tokens, top] int32 with their scores in weight [tokens, top] float32.  With
-    ``router`` None, ``x`` holds the logits themselves, float32 [tokens, experts]."""
-    _need_cuda(x, router, choice, weight)
+    ``router`` None, ``x`` holds the logits themselves, float32 [tokens, experts].  ``bias`` (float32
+    [experts]) is added to the logits before they are scored."""
+    _need_cuda(x, router, choice, weight, bias)
+    if bias is not None and (bias.dtype != torch.float32 or not bias.is_contiguous() or bias.numel() != x.shape[1] and router is None):
+        raise KernelError("moe_route: the bias is contiguous float32 [experts]")
     if router is None:
         if x.dtype != torch.float32:
             raise KernelError("moe_route: logits handed in must be float32")
@@ -929,11 +1083,11 @@ def moe_route(x: torch.Tensor, router: Optional[torch.Tensor], choice: torch.Ten
             or x.stride(1) != 1 or (router is not None and not router.is_contiguous()):
         raise KernelError("moe_route: experts must divide into the groups; choice int32, weight float32")
     f = _fn(_moe(), "rl_moe_route", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                      c_int, c_int, c_int, c_void_p, c_void_p, c_void_p])
+                                      c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
     _check(f(_ptr(x), _code(x.dtype), x.stride(0), _ptr(router), _code(router.dtype) if router is not None else 0,
              tokens, width, experts,
-             max(groups, 1), keep, group_top, top, 1 if softmax else 0, 1 if renorm else 0, _ptr(choice), _ptr(weight),
-             _stream()), "moe_route")
+             max(groups, 1), keep, group_top, top, 1 if softmax else 0, 1 if renorm else 0, _ptr(bias), _ptr(choice),
+             _ptr(weight), _stream()), "moe_route")
 
 
 def moe_group(choice: torch.Tensor, pairs: int, experts: int, order: torch.Tensor, tile_expert: torch.Tensor,
@@ -1010,7 +1164,7 @@ def gather_logprob(logits: torch.Tensor, rows: int, target: torch.Tensor, out: t
 
 
 def build_all(head_dims=(64, 128), maps_dims=((64, 128, 2), (128, 128, 1)), linear_dims=(64,), memory_dims=(64,),
-              verbose: bool = True) -> None:
+              delta_dims=(128,), verbose: bool = True) -> None:
     """Compiles every kernel family (attention for the given head sizes, attention with score maps for the
     given (key size, value size, maps), linear attention and the matrix memory for the given key sizes) and
     removes built files of these modules that belong to other versions of the sources."""
@@ -1023,6 +1177,7 @@ def build_all(head_dims=(64, 128), maps_dims=((64, 128, 2), (128, 128, 1)), line
         build.compile_module("sampling", "sampling.cu", verbose=verbose),
         build.compile_module("rowwise", "rowwise.cu", verbose=verbose),
         build.compile_module("moe", "moe.cu", verbose=verbose),
+        build.compile_module("stream_ops", "stream_ops.cu", verbose=verbose),
         build.compile_module("host_core", "host_core.cpp", verbose=verbose),   # host-only: cache manager, batch filler
     ]
     for d in head_dims:
@@ -1035,4 +1190,6 @@ def build_all(head_dims=(64, 128), maps_dims=((64, 128, 2), (128, 128, 1)), line
                                           verbose=verbose))
     for d in memory_dims:
         built.append(build.compile_module(f"matrix_memory_d{d}", "matrix_memory.cu", {"RL_MM_DIM": d}, verbose=verbose))
+    for d in delta_dims:
+        built.append(build.compile_module(f"delta_rule_d{d}", "delta_rule.cu", {"RL_DELTA_DIM": d}, verbose=verbose))
     build.remove_other_versions(built)

@@ -15,7 +15,9 @@ softmax's denominator without a key or a value; an output gate sigmoid(W_g h) pe
 before the output projection (W_g is then the fourth block of the fused projection); and a blend of the
 values with those that an earlier layer of the model computed for the same token (``value_mix`` "keep" in
 the layer that provides them, "blend" in those that use them: v <- (1 - lam) v + lam v_first; what is blended
-is what is cached).
+is what is cached).  ``conv_taps``: a short causal convolution over time on every channel of q, k and v
+directly behind the projection (and its biases), whose last inputs are the mixer's per-request state;
+``out_bias``: a bias on the output projection; a ``rope_halves`` encoding pairs entry i with entry i + half.
 
 The cache holds keys [kv_heads * maps, dim] and values [kv_heads, vdim] per token (a window group that
 keeps its first pages); sequences that bring one token go to the partitioned decode kernel, longer
@@ -33,7 +35,7 @@ import torch
 from ..ops import kernels
 from ..ops.linear import linear
 from .base import LayerCache, Mixer, build_part, op_mark, register
-from .spec import CacheSpec, CacheTensor, PartSpec, TensorSpec
+from .spec import CacheSpec, CacheTensor, PartSpec, StateSpec, TensorSpec
 
 
 @dataclass(frozen=True)
@@ -59,6 +61,8 @@ class MapsAttentionParams:
     gate: str = "none"           # none | head | entry: the output times sigmoid(W_g h)
     value_mix: str = "none"      # none | keep | blend (see above)
     value_mix_key: str = "v"     # layers that share values name the same key
+    conv_taps: int = 0           # > 0: a causal convolution over time on every channel of q, k and v, behind the projection
+    out_bias: bool = False       # the output projection has a bias
 
 
 @register("mixer", "maps_attention")
@@ -73,12 +77,14 @@ class MapsAttention(Mixer):
         if not (1 <= p.dim <= 256 and 1 <= p.vdim <= 256):
             raise ValueError(f"attention_maps kernels take key and value sizes up to 256; got dim={p.dim}, vdim={p.vdim}")
         self.position = build_part("position", p.position, rt) if p.position is not None else None
-        self.rotary = None           # (cos, sin) of an encoding that rotates neighbouring pairs
+        self.rotary = None           # (cos, sin) of an encoding whose pairs the head kernel rotates
+        self.halves = False          # ... entry i with entry i + half instead of its neighbour
         if self.position is not None and self.position.rotary_tables() is not None:
-            if getattr(self.position, "pairing", None) != "neighbours":
-                raise ValueError("maps_attention rotates neighbouring pairs (rope_pairs) or applies a position "
-                                 "encoding through its apply(); tables that pair entry i with i + D/2 are for "
-                                 "the attention part whose cache-write kernel rotates")
+            if getattr(self.position, "pairing", None) not in ("neighbours", "halves"):
+                raise ValueError("maps_attention rotates the first entries of a head in neighbouring pairs "
+                                 "(rope_pairs) or entry i with entry i + half (rope_halves), or applies a position "
+                                 "encoding through its apply()")
+            self.halves = self.position.pairing == "halves"
             self.rotary = self.position.rotary_tables()
             if 2 * self.rotary[0].shape[1] > p.dim:
                 raise ValueError(f"a rotation of {2 * self.rotary[0].shape[1]} entries does not fit heads of {p.dim}")
@@ -99,6 +105,18 @@ class MapsAttention(Mixer):
         self.proj_size = self.qkv_size + self.gate_size
         self.lam = 0.0
         self.mix = 0.0
+        if p.conv_taps < 0 or p.conv_taps > kernels.MAX_CONV_TAPS:
+            raise ValueError(f"a short convolution has up to {kernels.MAX_CONV_TAPS} taps; got {p.conv_taps}")
+
+    def state_spec(self):
+        """The convolution's last taps - 1 inputs of every q, k and v channel."""
+        p = self.params
+        if p.conv_taps > 1:
+            return StateSpec(((p.conv_taps - 1) * self.qkv_size,), "float32")
+        return None
+
+    def state_in_graphs(self) -> bool:
+        return True
 
     def cache_spec(self) -> CacheSpec:
         p = self.params
@@ -133,10 +151,18 @@ class MapsAttention(Mixer):
             t["g"] = TensorSpec((self.gate_size, p.hidden_size))
         if p.value_mix != "none":            # (the layer that provides the values may have the number too: unused)
             t["vmix"] = TensorSpec((), optional=p.value_mix == "keep")
+        if p.conv_taps > 0:
+            t.update({"q_conv": TensorSpec((self.q_size, p.conv_taps)), "k_conv": TensorSpec((self.k_size, p.conv_taps)),
+                      "v_conv": TensorSpec((self.v_size, p.conv_taps))})
+        if p.out_bias:
+            t["o_bias"] = TensorSpec((p.hidden_size,))
         return t
 
     def fused(self) -> Dict[str, list]:
-        return {"qkv": ["q", "k", "v"] + (["g"] if self.params.gate != "none" else [])}
+        out = {"qkv": ["q", "k", "v"] + (["g"] if self.params.gate != "none" else [])}
+        if self.params.conv_taps > 0:
+            out["qkv_conv"] = ["q_conv", "k_conv", "v_conv"]
+        return out
 
     # -- what a mixer that runs beside another one under a common output projection is asked for
     def inner_size(self) -> int:
@@ -144,6 +170,9 @@ class MapsAttention(Mixer):
 
     def out_weight(self) -> torch.Tensor:
         return self.w_o
+
+    def out_bias(self) -> Optional[torch.Tensor]:
+        return self.b_o
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
         p = self.params
@@ -154,6 +183,11 @@ class MapsAttention(Mixer):
             dt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
             self.w_qkv = torch.cat([w.to(dt) for w in ws], dim=0).contiguous()
         self.w_o = tensors["o"]
+        self.b_o = tensors["o_bias"].float().contiguous() if p.out_bias else None
+        self.w_conv = None
+        if p.conv_taps > 0:
+            self.w_conv = tensors["qkv_conv"] if "qkv_conv" in tensors else \
+                torch.cat([tensors[n] for n in ("q_conv", "k_conv", "v_conv")], dim=0).contiguous()
         self.b_qkv = None
         if p.bias:
             self.b_qkv = torch.cat([tensors[n].float() for n in ("q_bias", "k_bias", "v_bias")]).contiguous()
@@ -179,6 +213,8 @@ class MapsAttention(Mixer):
         self.forward_inner(x, ctx, cache, state, attn)
         out = rt.workspace.get("mixer.out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
         linear(attn, self.w_o, out)
+        if self.b_o is not None:
+            kernels.bias_act(out, self.b_o, kernels.ACT_NONE)
         op_mark(ctx, "o_proj", self.w_o, T)
         return out
 
@@ -190,7 +226,14 @@ class MapsAttention(Mixer):
         ws = rt.workspace
         qkv = ws.get("mattn.qkv", (rt.max_tokens, self.proj_size), rt.dtype)[:T]
         linear(x, self.w_qkv, qkv)
-        if self.b_qkv is not None:
+        gate_buf = qkv                     # where the gate's columns lie
+        if self.w_conv is not None:
+            # (the biases are added on the way into the convolution, whose state keeps the biased inputs)
+            conv = ws.get("mattn.qkv_conv", (rt.max_tokens, self.proj_size), rt.dtype)[:T]
+            kernels.short_conv(qkv, 0, self.w_conv, self.b_qkv, conv, 0, kernels.ACT_NONE, ctx.seq_of_token,
+                               ctx.state_slot, state, T)
+            qkv = conv
+        elif self.b_qkv is not None:
             kernels.bias_act(qkv, self.b_qkv, kernels.ACT_NONE, cols=self.qkv_size)
         op_mark(ctx, "qkv_proj", self.w_qkv, T)
         if self.position is not None and self.rotary is None:
@@ -206,7 +249,8 @@ class MapsAttention(Mixer):
             kernels.head_prep(qkv, ctx.positions, T, 0, p.num_heads * p.maps, self.q_size, p.num_kv_heads * p.maps, p.dim,
                               ctx.status, self.w_qnorm, self.w_knorm, self.norm_mode, p.eps, cos, sin,
                               self.q_size + self.k_size, self.v_size, v_first, self.mix_mode, self.mix,
-                              g.slots if cache.write else None, cache.tensors["k"], cache.tensors["v"], rt.page_size)
+                              g.slots if cache.write else None, cache.tensors["k"], cache.tensors["v"], rt.page_size,
+                              halves=self.rotary is not None and self.halves)
             op_mark(ctx, "qk_norm+rotate+kv_write", nbytes=(2.0 * self.qkv_size + self.k_size + self.v_size) * T * qkv.element_size())
             stored = True
         else:
@@ -219,7 +263,7 @@ class MapsAttention(Mixer):
             kernels.cache_store(qkv, self.q_size + self.k_size, p.num_kv_heads, p.vdim, g.slots, v_cache,
                                 rt.page_size, ctx.status, tokens=T)
             op_mark(ctx, "kv_write", nbytes=2.0 * T * (self.k_size + self.v_size) * qkv.element_size())
-        gate = qkv[:, self.qkv_size:] if self.gate_mode else None
+        gate = gate_buf[:, self.qkv_size:] if self.gate_mode else None
         common = (p.num_heads, p.num_kv_heads, p.dim, p.vdim, p.maps, rt.page_size, p.window, p.keep_first,
                   self.scale, p.softcap, self.lam, p.post_scale * scale, p.eps, p.unit_norm, self.sink, gate,
                   self.gate_mode)

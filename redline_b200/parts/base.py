@@ -24,6 +24,7 @@ from .spec import CacheSpec, PartSpec, StateSpec, TensorSpec
 
 _REGISTRIES: Dict[str, Dict[str, type]] = {
     "norm": {}, "mixer": {}, "ffn": {}, "position": {}, "block": {}, "embedding": {}, "head": {},
+    "connection": {},
 }
 
 
@@ -215,7 +216,8 @@ class Mixer(Part):
     def cache_spec(self) -> Optional[CacheSpec]:
         return None
 
-    def state_spec(self) -> Optional[StateSpec]:
+    def state_spec(self):
+        """None, one ``StateSpec``, or a tuple of them (the calls then get a tuple of pools)."""
         return None
 
     def state_in_graphs(self) -> bool:
@@ -303,8 +305,12 @@ class Block:
         """``ffn_norm`` and ``ffn`` are None for a layer that has a mixer only."""
         self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, self.rt = mixer_norm, mixer, ffn_norm, ffn, rt
 
+    mixer_conn = None        # set by the model builder for arrangements with several residual streams
+    ffn_conn = None
+
     def parts(self) -> List[Part]:
-        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn) if p is not None]
+        return [p for p in (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn, self.mixer_conn, self.ffn_conn)
+                if p is not None]
 
     def first_norm(self) -> Optional[Norm]:
         """The norm this block applies to the incoming stream first, if the block before may hand it

@@ -1,8 +1,8 @@
 """Gated feed-forward: down(act(gate(x)) * up(x)), gate and up fused into one
 projection [gate | up]; act is SiLU (reference: src/cuda/model/llama.cpp:134-136,
 src/cuda/kernels/elementwise.cu:66-82) unless the parameters name another activation
-(``gelu_tanh`` and the others of ``kernels.ACTIVATIONS``), which runs as a kernel of its
-own behind the product; prompt portions have the tcgen05 kernel's gated epilogue for SiLU and
+(``gelu_tanh`` and the others of ``kernels.ACTIVATIONS``, or ``clamped_swish``: gate and up clamped,
+g * sigmoid(slope * g) * (up + 1)), which runs as a kernel of its own behind the product; prompt portions have the tcgen05 kernel's gated epilogue for SiLU and
 the tanh GELU, and so has the weight-streaming product for at most 16 rows; the forms that also
 fuse the norm before and the add behind are SiLU's."""
 
@@ -29,7 +29,9 @@ class GatedMLPParams:
     hidden_size: int
     intermediate_size: int
     bias: bool = False
-    activation: str = "silu"
+    activation: str = "silu"       # or another of kernels.ACTIVATIONS, or "clamped_swish" (below)
+    limit: float = 0.0             # clamped_swish: g = min(gate, limit), u = clamp(up, -limit, limit),
+    slope: float = 1.0             #                act = g * sigmoid(slope * g) * (u + 1)
 
 
 @register("ffn", "swiglu_mlp")
@@ -47,9 +49,12 @@ class SwiGLUMLP(FeedForward):
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
-        if self.params.activation not in kernels.ACTIVATIONS:
+        self.clamped = self.params.activation == "clamped_swish"
+        if self.params.activation not in kernels.ACTIVATIONS and not self.clamped:
             raise ValueError(f"gated feed-forward: activation '{self.params.activation}' is not known "
-                             f"({sorted(kernels.ACTIVATIONS)})")
+                             f"({sorted(kernels.ACTIVATIONS) + ['clamped_swish']})")
+        if self.clamped and not self.params.limit > 0:
+            raise ValueError("gated feed-forward: clamped_swish needs a positive limit")
         self.silu = self.params.activation == "silu"
 
     def fused(self) -> Dict[str, list]:
@@ -93,6 +98,8 @@ class SwiGLUMLP(FeedForward):
                 kernels.add_bias(gu, self.b_gate_up)
             if self.silu:
                 kernels.swiglu(gu, act)
+            elif self.clamped:
+                kernels.gated_act(gu, act, kernels.ACT_CLAMPED_SWISH, p.limit, p.slope)
             else:
                 kernels.gated_act(gu, act, kernels.ACTIVATIONS[self.params.activation])
         op_mark(ctx, "gate_up+swiglu" if self.silu else "gate_up+act", self.w_gate_up, T)

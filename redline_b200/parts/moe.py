@@ -1,5 +1,6 @@
 """Feed-forwards without a gate, W_down f(W_up h), alone ("act_mlp") or as a mixture of experts
-("routed_experts"): a router scores the experts per token in float32 (sigmoid or softmax), experts lie in
+("routed_experts", whose experts may also be gated, W_down (f(W_gate h) * (W_up h)), and whose router may
+have a bias): a router scores the experts per token in float32 (sigmoid or softmax), experts lie in
 equal groups of neighbours of which only the best ``group_keep`` (by the sum of their ``group_top`` best
 scores) can be chosen, the ``top`` best experts of those run for the token, weighted by their scores
 (as they are, or divided by their sum), and a shared expert of the same form may run for every token.
@@ -74,6 +75,8 @@ class RoutedExpertsParams:
     activation: str = "gelu"
     shared_intermediate_size: int = 0    # 0: no shared expert
     shared_activation: Optional[str] = None
+    gated: bool = False                  # experts are W_down (f(W_gate h) * (W_up h)) instead of W_down f(W_up h)
+    router_bias: bool = False            # a bias on the router's logits
 
 
 @register("ffn", "routed_experts")
@@ -98,7 +101,11 @@ class RoutedExperts(FeedForward):
     def tensors(self) -> Dict[str, TensorSpec]:
         p = self.params
         t = {"router": TensorSpec((p.num_experts, p.hidden_size))}
+        if p.router_bias:
+            t["router_bias"] = TensorSpec((p.num_experts,))
         for e in range(p.num_experts):
+            if p.gated:
+                t[f"gate{e}"] = TensorSpec((p.intermediate_size, p.hidden_size))
             t[f"up{e}"] = TensorSpec((p.intermediate_size, p.hidden_size))
             t[f"down{e}"] = TensorSpec((p.hidden_size, p.intermediate_size))
         if self.shared is not None:
@@ -108,6 +115,9 @@ class RoutedExperts(FeedForward):
 
     def fused(self) -> Dict[str, list]:
         n = self.params.num_experts
+        if self.params.gated:      # every expert's gate rows, then its up rows
+            return {"up_all": [f"{m}{e}" for e in range(n) for m in ("gate", "up")],
+                    "down_all": [f"down{e}" for e in range(n)]}
         return {"up_all": [f"up{e}" for e in range(n)], "down_all": [f"down{e}" for e in range(n)]}
 
     def load(self, tensors: Dict[str, torch.Tensor]) -> None:
@@ -116,11 +126,13 @@ class RoutedExperts(FeedForward):
         def stacked(fused_name: str, stem: str) -> torch.Tensor:
             if fused_name in tensors:
                 return tensors[fused_name]
-            ws = [tensors[f"{stem}{e}"] for e in range(p.num_experts)]
+            stems = ("gate", "up") if (p.gated and stem == "up") else (stem,)
+            ws = [tensors[f"{m}{e}"] for e in range(p.num_experts) for m in stems]
             dt = torch.float32 if any(w.dtype == torch.float32 for w in ws) else ws[0].dtype
             return torch.cat([w.to(dt) for w in ws], dim=0).contiguous()
 
-        self.w_up = stacked("up_all", "up")            # [experts * ff, hidden]
+        self.w_up = stacked("up_all", "up")            # [experts * ff, hidden] (gated: [experts * 2 ff, hidden])
+        self.b_router = tensors["router_bias"].float().contiguous() if p.router_bias else None
         self.w_down = stacked("down_all", "down")      # [experts * hidden, ff]
         self.w_router = tensors["router"]
         if self.shared is not None:
@@ -149,7 +161,7 @@ class RoutedExperts(FeedForward):
         logits = ws.get("moe.logits", (rt.max_tokens, p.num_experts), torch.float32)[:T]
         linear(x, self.w_router, logits)
         kernels.moe_route(logits, None, choice, weight, T, p.groups, p.group_keep, p.group_top, p.top,
-                          softmax=p.score == "softmax", renorm=p.renormalize)
+                          softmax=p.score == "softmax", renorm=p.renormalize, bias=self.b_router)
         kernels.moe_group(choice, pairs, p.num_experts, order, tile_expert, tile_begin, tile_rows, meta)
         op_mark(ctx, "route", self.w_router, T)
         if x.dtype != self.w_up.dtype:
@@ -157,12 +169,18 @@ class RoutedExperts(FeedForward):
         act = ws.get("moe.act", (max_pairs, p.intermediate_size), rt.dtype)[:pairs]
         y = ws.get("moe.y", (max_pairs, p.hidden_size), rt.dtype)[:pairs]
         lists = (order, tile_expert, tile_begin, tile_rows, meta, max_tiles)
-        kernels.moe_gemm(x, p.top, self.w_up, act, *lists, act=self.act)
+        if p.gated:
+            gu = ws.get("moe.gate_up", (max_pairs, 2 * p.intermediate_size), rt.dtype)[:pairs]
+            kernels.moe_gemm(x, p.top, self.w_up, gu, *lists)
+            kernels.gated_act(gu, act, self.act)
+        else:
+            kernels.moe_gemm(x, p.top, self.w_up, act, *lists, act=self.act)
         kernels.moe_gemm(act, 1, self.w_down, y, *lists)
         elem = x.element_size()
-        op_mark(ctx, "experts", nbytes=float(min(pairs, p.num_experts) * 2 * p.intermediate_size * p.hidden_size * elem
-                                             + pairs * (2 * p.intermediate_size + 2 * p.hidden_size) * elem),
-                flops=4.0 * pairs * p.intermediate_size * p.hidden_size)
+        mats = 3 if p.gated else 2
+        op_mark(ctx, "experts", nbytes=float(min(pairs, p.num_experts) * mats * p.intermediate_size * p.hidden_size * elem
+                                             + pairs * (mats * p.intermediate_size + 2 * p.hidden_size) * elem),
+                flops=2.0 * mats * pairs * p.intermediate_size * p.hidden_size)
         shared = self.shared.run(x, ctx, "moe.shared") if self.shared is not None else None
         out = ws.get("ffn.out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
         kernels.moe_combine(y, weight, shared, out, T, p.top)

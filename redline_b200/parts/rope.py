@@ -116,3 +116,72 @@ class RotaryPairs(PositionEncoding):
 
     def nbytes(self) -> int:
         return 2 * self.cos.numel() * 4
+
+
+@dataclass(frozen=True)
+class RotaryHalvesParams:
+    """Rotation of the first ``dims`` entries of a head, entry i paired with entry i + dims / 2, with optional
+    YaRN scaling of the frequencies (``factor`` 0 or 1: none)."""
+
+    dims: int
+    base: float
+    max_positions: int
+    factor: float = 0.0        # YaRN: how far the context is stretched
+    original: int = 0          # the context length the frequencies were made for
+    fast: float = 32.0         # pairs that turn at least so often within ``original`` keep their frequency
+    slow: float = 1.0          # pairs that turn at most so often are divided by ``factor``
+
+
+def yarn_frequencies(p: RotaryHalvesParams) -> Tuple[List[float], float]:
+    """(frequency of every pair, factor on cos and sin).  With f_i = base^(-2i/dims) and
+    index(turns) = dims ln(original / (2 pi turns)) / (2 ln base): lo = max(floor(index(fast)), 0),
+    hi = min(ceil(index(slow)), dims - 1), ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1); pair i turns at
+    f_i / factor * ramp_i + f_i (1 - ramp_i), and cos and sin are multiplied by 0.1 ln(factor) + 1."""
+    half = p.dims // 2
+    f = [float(p.base) ** (-2.0 * i / p.dims) for i in range(half)]
+    if not p.factor or p.factor == 1.0:
+        return f, 1.0
+
+    def index(turns: float) -> float:
+        return p.dims * math.log(p.original / (2.0 * math.pi * turns)) / (2.0 * math.log(p.base))
+
+    lo = max(math.floor(index(p.fast)), 0)
+    hi = min(math.ceil(index(p.slow)), p.dims - 1)
+    out = []
+    for i in range(half):
+        ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+        out.append(f[i] / p.factor * ramp + f[i] * (1.0 - ramp))
+    return out, 0.1 * math.log(p.factor) + 1.0
+
+
+_half_tables = {}
+
+
+@register("position", "rope_halves")
+class RotaryHalves(PositionEncoding):
+    """Tables [positions, dims / 2] of cos and sin (float32 of angles formed in double precision, the YaRN
+    factor multiplied in); the mixer's kernel pairs entry i with entry i + dims / 2."""
+
+    pairing = "halves"
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        p = self.params
+        if p.dims <= 0 or p.dims % 2 != 0:
+            raise ValueError(f"rope_halves rotates an even number of entries, got {p.dims}")
+        if p.factor and p.factor != 1.0 and (p.factor < 0 or p.original <= 0 or p.fast <= 0 or p.slow <= 0 or p.base <= 1):
+            raise ValueError("rope_halves: a scaling needs positive factor, original, fast and slow and a base above 1")
+        n = max(min(p.max_positions, rt.max_seq_len) if rt.max_seq_len > 0 else p.max_positions, 1)
+        key = (p, n, str(rt.device))
+        if key not in _half_tables:
+            freq, mag = yarn_frequencies(p)
+            angle = np.arange(n, dtype=np.float64)[:, None] * np.asarray(freq, dtype=np.float64)[None, :]
+            _half_tables[key] = (torch.from_numpy((np.cos(angle) * mag).astype(np.float32)).to(rt.device),
+                                 torch.from_numpy((np.sin(angle) * mag).astype(np.float32)).to(rt.device))
+        self.cos, self.sin = _half_tables[key]
+
+    def rotary_tables(self):
+        return self.cos, self.sin
+
+    def nbytes(self) -> int:
+        return 2 * self.cos.numel() * 4

@@ -40,6 +40,9 @@ class LayerSpec:
     # for arrangements that also norm what a sublayer puts out, before it is added to the stream
     mixer_post_norm: Optional[PartSpec] = None
     ffn_post_norm: Optional[PartSpec] = None
+    # for arrangements that keep several residual streams: how each sublayer reads them and writes them back
+    mixer_conn: Optional[PartSpec] = None
+    ffn_conn: Optional[PartSpec] = None
 
 
 @dataclass(frozen=True)
@@ -128,7 +131,9 @@ class CacheSpec:
 
 @dataclass(frozen=True)
 class StateSpec:
-    """Per-request state of fixed size that a mixer keeps (none for attention)."""
+    """Per-request state of fixed size that a mixer keeps (none for attention).  A mixer may name several
+    (``Mixer.state_spec`` then returns a tuple): each becomes a pool of its own, and the mixer's calls receive the
+    pools as a tuple in the same order."""
 
     shape: Tuple[int, ...]
     dtype: str = "float32"

@@ -1,5 +1,5 @@
 """Prefill and decode throughput of one architecture beside another at equal layer sizes, with the
-per-op roofline fractions of both (``bench.py --compare-design kapitar`` or ``pufevik``).
+per-op roofline fractions of both (``bench.py --compare-design kapitar``, ``pufevik`` or ``vizotar``).
 
 Every size is a handful of layers whose matrices have the shapes of a real model's (random weights):
 the Kapitar model has one layer of every kind (attention + dense, lightning + routed, attention + routed,
@@ -13,6 +13,14 @@ each op's bytes and operations against the measured copy bandwidth and matrix-pr
 The Pufevik model has two layers of each kind (a pair of windowed attention with a sink beside a matrix
 memory, and gated full attention with blended values; every layer with a gated feed-forward), the Llama
 model beside it the same width, number of layers, heads, kv heads, head size and feed-forward width.
+
+The Vizotar model has four layers on four residual streams: a pair (windowed attention with a sink, short
+convolutions and YaRN rotation, beside a matrix memory) with a dense feed-forward, the gated delta rule with
+routed experts, a pair with routed experts, the delta rule with a dense feed-forward.  Beside it stands
+Pufevik, the closest architecture the package has (the same pair without convolutions on one stream, full
+attention where Vizotar has the delta rule, dense feed-forwards), at the same width, heads, head sizes,
+window, memory sizes and feed-forward width; the routed layers' chosen experts together are as wide as the
+dense feed-forward.
 """
 
 from __future__ import annotations
@@ -33,6 +41,15 @@ PUFEVIK_SIZES: Dict[str, Dict[str, int]] = {
     # width, heads / kv heads / key and value size of both kinds of attention, feed-forward width, the memory's heads and sizes
     "s": dict(width=1024, heads=8, kv_heads=2, dim=128, vdim=128, ff=2816, mem_heads=8, mem_dim=64, mem_vdim=128, vocab=32000),
     "m": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, ff=5632, mem_heads=16, mem_dim=64, mem_vdim=128, vocab=32000),
+}
+VIZOTAR_SIZES: Dict[str, Dict[str, int]] = {
+    # as PUFEVIK_SIZES, plus the delta rule's heads and sizes, the inner sizes of its low-rank projections, the experts
+    "s": dict(width=1024, heads=8, kv_heads=2, dim=128, vdim=128, ff=2816, mem_heads=8, mem_dim=64, mem_vdim=128,
+              delta_heads=8, delta_qk_heads=4, delta_dim=128, delta_vdim=128, rank=64, experts=16, top=4, expert_ff=704,
+              streams=4, taps=4, vocab=32000),
+    "m": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, ff=5632, mem_heads=16, mem_dim=64, mem_vdim=128,
+              delta_heads=16, delta_qk_heads=8, delta_dim=128, delta_vdim=128, rank=128, experts=32, top=4, expert_ff=1408,
+              streams=4, taps=4, vocab=32000),
 }
 WINDOW, KEEP_FIRST = 1024, 4
 PROMPT = 2048
@@ -78,7 +95,25 @@ def llama_beside_pufevik(s: Dict[str, int]) -> Dict[str, Any]:
             "rms_norm_eps": 1e-5, "tie_word_embeddings": False, "max_position_embeddings": 8192, "hidden_act": "silu"}
 
 
-DESIGNS = {"kapitar": (SIZES, kapitar_config, llama_config), "pufevik": (PUFEVIK_SIZES, pufevik_config, llama_beside_pufevik)}
+def vizotar_config(s: Dict[str, int]) -> Dict[str, Any]:
+    left = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["vdim"], "scale": s["dim"] ** -0.5,
+            "mask": {"size": WINDOW}, "conv": s["taps"],
+            "rot": {"base": 1000000.0, "dims": s["dim"] // 2,
+                    "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    pair = {"left": left, "right": {"heads": s["mem_heads"], "dim": s["mem_dim"], "vdim": s["mem_vdim"], "gate_cap": 12.0}}
+    delta = {"heads": s["delta_heads"], "kv_heads": s["delta_qk_heads"], "dim": s["delta_dim"], "vdim": s["delta_vdim"],
+             "conv": s["taps"], "decay_rank": s["rank"], "gate_rank": s["rank"]}
+    dense = {"kind": "dense", "ff": s["ff"], "limit": 7.0}
+    moe = {"kind": "moe", "expert": {"ff": s["expert_ff"]}, "router": {"experts": s["experts"], "top": s["top"]}}
+    return {"architecture": "Vizotar", "vocab": s["vocab"], "width": s["width"], "streams": s["streams"], "norm": {"eps": 1e-6},
+            "layers": [{"type": "parallel", "mixer": pair, "mlp": dense}, {"type": "channel_delta", "mixer": delta, "mlp": moe},
+                       {"type": "parallel", "mixer": pair, "mlp": moe}, {"type": "channel_delta", "mixer": delta, "mlp": dense}]}
+
+
+# design -> (its sizes, its configuration, the architecture beside it, that one's configuration at the same sizes)
+DESIGNS = {"kapitar": (SIZES, kapitar_config, "llama", llama_config),
+           "pufevik": (PUFEVIK_SIZES, pufevik_config, "llama", llama_beside_pufevik),
+           "vizotar": (VIZOTAR_SIZES, vizotar_config, "pufevik", pufevik_config)}
 
 
 def _prefill(model: str, tokens: int, reps: int, warmup: int) -> float:
@@ -177,8 +212,8 @@ def compare(design: str, sizes: List[str], steps: int, warmup: int, batch: int, 
     from ..weights import write_random_model
     if design not in DESIGNS:
         raise ValueError(f"no comparison is defined for '{design}' ({', '.join(DESIGNS)})")
-    table, design_config, beside_config = DESIGNS[design]
-    out: Dict[str, Any] = {"design": design, "beside": "llama", "prompt_tokens": PROMPT, "decode_batch": batch,
+    table, design_config, beside, beside_config = DESIGNS[design]
+    out: Dict[str, Any] = {"design": design, "beside": beside, "prompt_tokens": PROMPT, "decode_batch": batch,
                            "decode_prompt": DECODE_PROMPT, "dtype": "bf16", "data": "synthetic (random weights and tokens)",
                            "sizes": {}}
     with tempfile.TemporaryDirectory() as tmp:
@@ -187,7 +222,7 @@ def compare(design: str, sizes: List[str], steps: int, warmup: int, batch: int, 
             entry: Dict[str, Any] = {"shape": dict(s, layers=4, window=WINDOW)}
             if design == "kapitar":
                 entry["shape"]["keep_first"] = KEEP_FIRST
-            for arch, cfg in ((design, design_config(s)), ("llama", beside_config(s))):
+            for arch, cfg in ((design, design_config(s)), (beside, beside_config(s))):
                 d = os.path.join(tmp, f"{arch}_{name}")
                 t0 = time.time()
                 write_random_model(d, config_from_dict(cfg), seed=0)

@@ -230,6 +230,8 @@ class MapsAttention(Mixer):
         if self.w_conv is not None:
             # (the biases are added on the way into the convolution, whose state keeps the biased inputs)
             conv = ws.get("mattn.qkv_conv", (rt.max_tokens, self.proj_size), rt.dtype)[:T]
+            if state is None:          # one tap: a weight per channel, nothing carried
+                state = ws.get("mattn.no_state", (rt.max_seqs + 1, 1), torch.float32)
             kernels.short_conv(qkv, 0, self.w_conv, self.b_qkv, conv, 0, kernels.ACT_NONE, ctx.seq_of_token,
                                ctx.state_slot, state, T)
             qkv = conv

@@ -7,10 +7,12 @@
 //     o_t = S^T q_t                (the read-out sees the token's own write)
 //
 // S is [D, DV] per (request, head) in float32, in the request's state slot: zero for a new request,
-// carried from step to step.  Columns of S never mix, so a CTA owns 32 columns of one (sequence, head)
-// and walks the sequence's tokens in order; within a warp 8 columns x 4 groups of rows: a thread keeps
-// every fourth row of its column in registers and the two inner products are finished by two shuffles.
-// q, k and the decays of a few tokens at a time are staged in shared memory.  Everything here is float32:
+// carried from step to step.  Columns of S never mix, so a CTA owns a few columns of one (sequence, head)
+// and walks the sequence's tokens in order; within a warp 32 / G columns x G groups of rows (G = 4, or 8 from
+// key size 128 on: shorter chains per token and more CTAs): a thread keeps D / G neighbouring rows of its
+// column in registers, sums its part of the two inner products in four independent chains, and shuffles
+// finish them.  q, k and the decays of a few tokens at a time are staged in shared memory by asynchronous
+// copies into one of two buffers while the tokens of the other are worked on.  Everything here is float32:
 // q and k arrive as unit vectors, beta and the decays as numbers in (0, 1) (delta_prep_kernel makes them
 // from the projections); v is read in the activation type.
 //
@@ -28,11 +30,32 @@
 namespace rl {
 
 constexpr int kD = RL_DELTA_DIM;
-constexpr int kGroups = 4;                         // groups of rows a column is split into
-constexpr int kRows = (kD + kGroups - 1) / kGroups; // rows a thread keeps
+constexpr int kGroups = kD >= 128 ? 8 : 4;         // groups of rows a column is split into
+constexpr int kRows = ((kD + kGroups - 1) / kGroups + 3) / 4 * 4;  // rows a thread keeps (a multiple of 4: float4 loads)
 constexpr int kDP = kRows * kGroups;               // D rounded up; the rows beyond D stay zero
-constexpr int kCols = 32;                          // columns of a CTA (4 warps x 8)
-constexpr int kTok = 8;                            // tokens staged at a time
+constexpr int kStride = kRows + 4;                 // floats from one group's rows to the next in shared memory (spreads the banks)
+constexpr int kSm = kGroups * kStride;             // floats of one staged vector
+constexpr int kWarpCols = 32 / kGroups;            // columns of a warp
+constexpr int kCols = 4 * kWarpCols;               // columns of a CTA (4 warps)
+constexpr int kTok = kD > 128 ? 4 : 8;             // tokens staged at a time (two such buffers)
+constexpr int kThreads = 128;
+constexpr int kVPer = (kTok * kCols + kThreads - 1) / kThreads;   // values a thread fetches per staged batch
+constexpr bool kVec = kD % 4 == 0;                 // rows of q, k and the decays start on 16-byte boundaries
+
+// Sum over the lanes that hold the groups of one column (lanes c, c + kWarpCols, c + 2 kWarpCols, ...).
+__device__ __forceinline__ float column_sum(float v) {
+#pragma unroll
+  for (int off = kWarpCols; off < 32; off <<= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
+  return v;
+}
+
+__device__ __forceinline__ void async_copy4(float* dst, const float* src) {
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(dst))), "l"(src));
+}
+__device__ __forceinline__ void async_copy16(float* dst, const float* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(dst))), "l"(src));
+}
+__device__ __forceinline__ void async_copies_done() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 
 // First token index t in [0, n) with seq_of_token[t] >= s (sequences lie in order in a step).
 __device__ __forceinline__ int first_token_of(const int32_t* __restrict__ seq_of_token, int n, int s) {
@@ -59,23 +82,25 @@ struct DeltaArgs {
   long long slot_stride;   // floats from one slot to the next
   float* out;              // [tokens, heads * DV]
   int tokens, heads, qk_heads, dv;
+  int vec_ok;              // q, k and decay are 16-byte aligned
 };
 
+// Row r of a staged vector lies at (r / kRows) * kStride + r % kRows: a thread's rows are contiguous.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kThreads)
 delta_rule_kernel(const DeltaArgs<T> a) {
   pdl_launch();
   pdl_wait();
-  __shared__ float qs[kTok][kDP];
-  __shared__ float ks[kTok][kDP];
-  __shared__ float as[kTok][kDP];
-  __shared__ float vs[kTok][kCols];
-  __shared__ float bs[kTok];
+  __shared__ __align__(16) float qs[2][kTok][kSm];
+  __shared__ __align__(16) float ks[2][kTok][kSm];
+  __shared__ __align__(16) float as[2][kTok][kSm];
+  __shared__ float vs[2][kTok][kCols];
+  __shared__ float bs[2][kTok];
   const int seq = blockIdx.z, head = blockIdx.y;
   const int qk_head = head / (a.heads / a.qk_heads);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int group = lane >> 3;                                   // rows group, group + 4, group + 8, ...
-  const int local_col = warp * 8 + (lane & 7);
+  const int group = lane / kWarpCols;                            // rows group * kRows .. group * kRows + kRows - 1
+  const int local_col = warp * kWarpCols + (lane % kWarpCols);
   const int col = blockIdx.x * kCols + local_col;
   const bool mine = col < a.dv;
   const int t0 = first_token_of(a.seq_of_token, a.tokens, seq);
@@ -86,54 +111,114 @@ delta_rule_kernel(const DeltaArgs<T> a) {
   float S[kRows];
 #pragma unroll
   for (int i = 0; i < kRows; ++i) {
-    const int row = i * kGroups + group;
+    const int row = group * kRows + i;
     S[i] = (mine && row < kD) ? plane[static_cast<size_t>(row) * a.dv + col] : 0.f;
   }
-  for (int tb = t0; tb < t1; tb += kTok) {
-    const int nt = min(kTok, t1 - tb);
-    __syncthreads();
-    for (int i = threadIdx.x; i < nt * kDP; i += blockDim.x) {
-      const int tt = i / kDP, d = i - tt * kDP;
-      const size_t t = tb + tt;
-      const bool in = d < kD;
-      qs[tt][d] = in ? a.q[(t * a.qk_heads + qk_head) * kD + d] : 0.f;
-      ks[tt][d] = in ? a.k[(t * a.qk_heads + qk_head) * kD + d] : 0.f;
-      as[tt][d] = in ? a.decay[(t * a.heads + head) * kD + d] : 1.f;
+  if (kDP > kD) {          // the rows beyond D: k = q = 0 and decay 1, never overwritten
+    for (int i = threadIdx.x; i < 2 * kTok * kSm; i += kThreads) {
+      (&qs[0][0][0])[i] = 0.f;
+      (&ks[0][0][0])[i] = 0.f;
+      (&as[0][0][0])[i] = 1.f;
     }
-    for (int i = threadIdx.x; i < nt * kCols; i += blockDim.x) {
+    __syncthreads();
+  }
+  const bool vec = kVec && a.vec_ok;
+  // q, k and the decays of tokens tb .. tb + nt - 1 on their way into buffer b (asynchronous copies)
+  auto stage = [&](int b, int tb, int nt) {
+    if (vec) {
+      constexpr int per = kD / 4;
+      for (int i = threadIdx.x; i < nt * per; i += kThreads) {
+        const int tt = i / per, e = (i - tt * per) * 4;
+        const int sm = (e / kRows) * kStride + e % kRows;
+        const size_t t = tb + tt;
+        async_copy16(&qs[b][tt][sm], a.q + (t * a.qk_heads + qk_head) * kD + e);
+        async_copy16(&ks[b][tt][sm], a.k + (t * a.qk_heads + qk_head) * kD + e);
+        async_copy16(&as[b][tt][sm], a.decay + (t * a.heads + head) * kD + e);
+      }
+    } else {
+      for (int i = threadIdx.x; i < nt * kD; i += kThreads) {
+        const int tt = i / kD, e = i - tt * kD;
+        const int sm = (e / kRows) * kStride + e % kRows;
+        const size_t t = tb + tt;
+        async_copy4(&qs[b][tt][sm], a.q + (t * a.qk_heads + qk_head) * kD + e);
+        async_copy4(&ks[b][tt][sm], a.k + (t * a.qk_heads + qk_head) * kD + e);
+        async_copy4(&as[b][tt][sm], a.decay + (t * a.heads + head) * kD + e);
+      }
+    }
+  };
+  // the values and betas of a batch pass through registers (the values arrive in the activation type)
+  float vreg[kVPer], breg = 0.f;
+  auto fetch = [&](int tb, int nt) {
+#pragma unroll
+    for (int j = 0; j < kVPer; ++j) {
+      const int i = threadIdx.x + j * kThreads;
       const int tt = i / kCols, c = i - tt * kCols;
       const int gc = blockIdx.x * kCols + c;
-      vs[tt][c] = gc < a.dv ? to_float(a.v[static_cast<size_t>(tb + tt) * a.ld_v + head * a.dv + gc]) : 0.f;
+      vreg[j] = (tt < nt && gc < a.dv) ? to_float(a.v[static_cast<size_t>(tb + tt) * a.ld_v + head * a.dv + gc]) : 0.f;
     }
-    if (threadIdx.x < nt) bs[threadIdx.x] = a.beta[static_cast<size_t>(tb + threadIdx.x) * a.heads + head];
+    if (threadIdx.x < nt) breg = a.beta[static_cast<size_t>(tb + threadIdx.x) * a.heads + head];
+  };
+  auto put = [&](int b) {
+#pragma unroll
+    for (int j = 0; j < kVPer; ++j) {
+      const int i = threadIdx.x + j * kThreads;
+      if (i < kTok * kCols) (&vs[b][0][0])[i] = vreg[j];
+    }
+    if (threadIdx.x < kTok) bs[b][threadIdx.x] = breg;
+  };
+  {
+    const int nt = min(kTok, t1 - t0);
+    stage(0, t0, nt);
+    fetch(t0, nt);
+    put(0);
+    async_copies_done();
     __syncthreads();
+  }
+  int b = 0;
+  for (int tb = t0; tb < t1; tb += kTok, b ^= 1) {
+    const int nt = min(kTok, t1 - tb);
+    const int nn = min(kTok, t1 - tb - kTok);        // tokens of the batch after this one
+    if (nn > 0) {
+      stage(b ^ 1, tb + kTok, nn);
+      fetch(tb + kTok, nn);
+    }
     for (int tt = 0; tt < nt; ++tt) {
-      float sk = 0.f;
+      const float4* a4 = reinterpret_cast<const float4*>(&as[b][tt][group * kStride]);
+      const float4* k4 = reinterpret_cast<const float4*>(&ks[b][tt][group * kStride]);
+      const float4* q4 = reinterpret_cast<const float4*>(&qs[b][tt][group * kStride]);
+      float kk[kRows];
+      float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;     // independent chains
 #pragma unroll
-      for (int i = 0; i < kRows; ++i) {
-        const int row = i * kGroups + group;
-        S[i] *= as[tt][row];
-        sk = fmaf(S[i], ks[tt][row], sk);
+      for (int i = 0; i < kRows; i += 4) {
+        const float4 av = a4[i >> 2], kv = k4[i >> 2];
+        kk[i] = kv.x; kk[i + 1] = kv.y; kk[i + 2] = kv.z; kk[i + 3] = kv.w;
+        S[i] *= av.x;     p0 = fmaf(S[i], kv.x, p0);
+        S[i + 1] *= av.y; p1 = fmaf(S[i + 1], kv.y, p1);
+        S[i + 2] *= av.z; p2 = fmaf(S[i + 2], kv.z, p2);
+        S[i + 3] *= av.w; p3 = fmaf(S[i + 3], kv.w, p3);
       }
-      sk += __shfl_xor_sync(0xffffffffu, sk, 8);
-      sk += __shfl_xor_sync(0xffffffffu, sk, 16);
-      const float d = bs[tt] * (vs[tt][local_col] - sk);
-      float o = 0.f;
+      const float sk = column_sum((p0 + p1) + (p2 + p3));
+      const float d = bs[b][tt] * (vs[b][tt][local_col] - sk);
+      p0 = p1 = p2 = p3 = 0.f;
 #pragma unroll
-      for (int i = 0; i < kRows; ++i) {
-        const int row = i * kGroups + group;
-        S[i] = fmaf(ks[tt][row], d, S[i]);
-        o = fmaf(S[i], qs[tt][row], o);
+      for (int i = 0; i < kRows; i += 4) {
+        const float4 qv = q4[i >> 2];
+        S[i] = fmaf(kk[i], d, S[i]);             p0 = fmaf(S[i], qv.x, p0);
+        S[i + 1] = fmaf(kk[i + 1], d, S[i + 1]); p1 = fmaf(S[i + 1], qv.y, p1);
+        S[i + 2] = fmaf(kk[i + 2], d, S[i + 2]); p2 = fmaf(S[i + 2], qv.z, p2);
+        S[i + 3] = fmaf(kk[i + 3], d, S[i + 3]); p3 = fmaf(S[i + 3], qv.w, p3);
       }
-      o += __shfl_xor_sync(0xffffffffu, o, 8);
-      o += __shfl_xor_sync(0xffffffffu, o, 16);
+      const float o = column_sum((p0 + p1) + (p2 + p3));
       if (mine && group == 0) a.out[(static_cast<size_t>(tb + tt) * a.heads + head) * a.dv + col] = o;
     }
+    if (nn > 0) put(b ^ 1);
+    async_copies_done();
+    __syncthreads();
   }
   if (mine) {
 #pragma unroll
     for (int i = 0; i < kRows; ++i) {
-      const int row = i * kGroups + group;
+      const int row = group * kRows + i;
       if (row < kD) plane[static_cast<size_t>(row) * a.dv + col] = S[i];
     }
   }
@@ -249,7 +334,9 @@ int rl_delta_rule(int act_dtype, const float* q, const float* k, const void* v, 
     a.q = q; a.k = k; a.v = static_cast<const T*>(v); a.ld_v = ld_v; a.beta = beta; a.decay = decay;             \
     a.seq_of_token = seq_of_token; a.state_slot = state_slot; a.state = state; a.slot_stride = slot_stride;      \
     a.out = out; a.tokens = tokens; a.heads = heads; a.qk_heads = qk_heads; a.dv = dv;                           \
-    launch_kernel(delta_rule_kernel<T>, grid, dim3(128), 0, stream, a);                                          \
+    a.vec_ok = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |                               \
+                 reinterpret_cast<uintptr_t>(decay)) & 15) == 0;                                                 \
+    launch_kernel(delta_rule_kernel<T>, grid, dim3(kThreads), 0, stream, a);                                          \
   } while (0)
   if (act_dtype == RL_F32) RL_CASE(float);
   else RL_CASE(bf16);

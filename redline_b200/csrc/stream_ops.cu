@@ -9,9 +9,10 @@
 //   total given:    total = sum_s X_s   (what the model's final norm reads)
 // The row u lives in dynamic shared memory (width floats).
 //
-// pair_norm_mean_kernel, one CTA per token: out = ca * N(a, wa) + cb * N(b, wb), N the RMS norm.
+// pair_norm_mean_kernel, one CTA per token: out = ca * N(a + bias_a, wa) + cb * N(b + bias_b, wb), N the RMS
+// norm, the biases (float32, of the two products that made a and b) optional.
 //
-// short_conv_kernel, one thread per (token, channel): y_t = act(sum_j w[c, j] (u_(t - taps + 1 + j) + bias_c)),
+// short_conv_kernel, one thread per channel and eight tokens: y_t = act(sum_j w[c, j] (u_(t - taps + 1 + j) + bias_c)),
 // over the tokens of the token's own sequence; tokens before the step's portion come from the request's state
 // slot, which holds the last taps - 1 inputs (bias added) in float32: [taps - 1, channels], the oldest first,
 // zeros for a new request.  short_conv_state_kernel then moves the slot on: the thread of a sequence's last
@@ -117,7 +118,8 @@ __global__ void streams_step_kernel(const StreamsArgs a, const TA* __restrict__ 
 template <typename TA, typename TW>
 __global__ void pair_norm_mean_kernel(const TA* __restrict__ a, int ld_a, const TW* __restrict__ wa, float ca,
                                       const TA* __restrict__ b, int ld_b, const TW* __restrict__ wb, float cb,
-                                      TA* __restrict__ out, int ld_out, int width, float eps) {
+                                      TA* __restrict__ out, int ld_out, int width, float eps,
+                                      const float* __restrict__ bias_a, const float* __restrict__ bias_b) {
   pdl_launch();
   pdl_wait();
   __shared__ float red[32];
@@ -126,7 +128,8 @@ __global__ void pair_norm_mean_kernel(const TA* __restrict__ a, int ld_a, const 
   const TA* pb = b + t * ld_b;
   float sa = 0.f, sb = 0.f;
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
-    const float x = to_float(pa[c]), z = to_float(pb[c]);
+    const float x = to_float(pa[c]) + (bias_a != nullptr ? bias_a[c] : 0.f);
+    const float z = to_float(pb[c]) + (bias_b != nullptr ? bias_b[c] : 0.f);
     sa = fmaf(x, x, sa);
     sb = fmaf(z, z, sb);
   }
@@ -134,8 +137,11 @@ __global__ void pair_norm_mean_kernel(const TA* __restrict__ a, int ld_a, const 
   sb = block_sum(sb, red);
   const float ra = ca * rsqrtf(sa / static_cast<float>(width) + eps);
   const float rb = cb * rsqrtf(sb / static_cast<float>(width) + eps);
-  for (int c = threadIdx.x; c < width; c += blockDim.x)
-    out[t * ld_out + c] = from_float<TA>(to_float(pa[c]) * ra * to_float(wa[c]) + to_float(pb[c]) * rb * to_float(wb[c]));
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float x = to_float(pa[c]) + (bias_a != nullptr ? bias_a[c] : 0.f);
+    const float z = to_float(pb[c]) + (bias_b != nullptr ? bias_b[c] : 0.f);
+    out[t * ld_out + c] = from_float<TA>(x * ra * to_float(wa[c]) + z * rb * to_float(wb[c]));
+  }
 }
 
 struct ConvArgs {
@@ -147,58 +153,94 @@ struct ConvArgs {
   long long slot_stride;
 };
 
+constexpr int kConvTile = 8;         // tokens a thread of short_conv_kernel walks
+constexpr int kStateTile = 32;       // tokens a thread of short_conv_state_kernel looks at
+
+// Input u_s of channel c for the token at index s of the step, or, where s lies before the first token of
+// the sequence in this step (index `first`), what the sequence's slot holds for it.
+template <typename TA>
+__device__ __forceinline__ float conv_input(const ConvArgs& a, const TA* __restrict__ x, const float* st, int s,
+                                            int first, int c, float bias) {
+  if (s >= first) return to_float(x[static_cast<size_t>(s) * a.ld_x + a.col_x + c]) + bias;
+  return st[static_cast<size_t>(a.taps - 1 + (s - first)) * a.channels + c];
+}
+
+// Index of the first token of token t's sequence in this step, looking back at most `reach` tokens
+// (t - reach if the sequence began earlier: nothing before that is asked for).
+__device__ __forceinline__ int conv_first(const int32_t* __restrict__ seq_of_token, int t, int seq, int reach) {
+  int first = t;
+  while (first > 0 && t - first < reach && seq_of_token[first - 1] == seq) --first;
+  return first;
+}
+
+// One thread per channel and kConvTile consecutive tokens: the window of the last taps - 1 inputs slides in
+// registers from token to token and is gathered anew where another sequence begins.
 template <typename TA, typename TW>
 __global__ void short_conv_kernel(const ConvArgs a, const TA* __restrict__ x, const TW* __restrict__ w,
                                   TA* __restrict__ y) {
   pdl_launch();
   pdl_wait();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  const int t = blockIdx.y;
   if (c >= a.channels) return;
-  const int seq = a.seq_of_token[t];
+  const int t_begin = blockIdx.y * kConvTile, t_end = min(t_begin + kConvTile, a.tokens);
   const float bias = a.bias != nullptr ? a.bias[c] : 0.f;
-  const float* st = a.state + static_cast<size_t>(a.state_slot[seq]) * a.slot_stride;
-  float acc = 0.f;
-  int first = -1;                          // index of the first token of the sequence in this step, once known
-  for (int back = 0; back < a.taps; ++back) {        // the token itself, then the ones before it
-    const int s = t - back;
-    float u;
-    if (first < 0 && s >= 0 && a.seq_of_token[s] == seq) {
-      u = to_float(x[static_cast<size_t>(s) * a.ld_x + a.col_x + c]) + bias;
-    } else {
-      if (first < 0) first = s + 1;
-      u = st[static_cast<size_t>(a.taps - 1 + (s - first)) * a.channels + c];
-    }
-    acc = fmaf(to_float(w[static_cast<size_t>(c) * a.taps + (a.taps - 1 - back)]), u, acc);
+  const int keep = a.taps - 1;
+  float wt[kMaxTaps], win[kMaxTaps];     // win[j]: the input j + 1 tokens back, wt[j] its weight
+#pragma unroll
+  for (int j = 0; j < kMaxTaps; ++j) {
+    wt[j] = j < keep ? to_float(w[static_cast<size_t>(c) * a.taps + (keep - 1 - j)]) : 0.f;
+    win[j] = 0.f;
   }
-  if (a.act == ACT_SILU) acc = acc / (1.f + expf(-acc));
-  y[static_cast<size_t>(t) * a.ld_y + a.col_y + c] = from_float<TA>(acc);
+  const float w_now = to_float(w[static_cast<size_t>(c) * a.taps + keep]);
+  int seq = -1;
+  for (int t = t_begin; t < t_end; ++t) {
+    const int sq = a.seq_of_token[t];
+    if (sq != seq) {                     // the tile's first token, or another sequence begins: gather the window
+      seq = sq;
+      const int first = conv_first(a.seq_of_token, t, seq, keep);
+      const float* st = a.state + static_cast<size_t>(a.state_slot[seq]) * a.slot_stride;
+#pragma unroll
+      for (int j = 0; j < kMaxTaps; ++j)
+        if (j < keep) win[j] = conv_input(a, x, st, t - 1 - j, first, c, bias);
+    }
+    const float u = to_float(x[static_cast<size_t>(t) * a.ld_x + a.col_x + c]) + bias;
+    float acc = 0.f;
+#pragma unroll
+    for (int j = kMaxTaps - 1; j >= 0; --j)                  // the oldest input first, as a sum over the taps in order
+      if (j < keep) acc = fmaf(wt[j], win[j], acc);
+    acc = fmaf(w_now, u, acc);
+#pragma unroll
+    for (int j = kMaxTaps - 1; j > 0; --j) win[j] = win[j - 1];
+    win[0] = u;
+    if (a.act == ACT_SILU) acc = acc / (1.f + expf(-acc));
+    y[static_cast<size_t>(t) * a.ld_y + a.col_y + c] = from_float<TA>(acc);
+  }
 }
 
+// Moves the slots on: the thread that meets a sequence's last token of the step gathers the channel's last
+// taps - 1 inputs (from the step, or from the old slot where the portion is shorter) and writes them back.
 template <typename TA>
 __global__ void short_conv_state_kernel(const ConvArgs a, const TA* __restrict__ x) {
   pdl_launch();
   pdl_wait();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  const int t = blockIdx.y;
   if (c >= a.channels) return;
-  const int seq = a.seq_of_token[t];
-  if (t + 1 < a.tokens && a.seq_of_token[t + 1] == seq) return;      // not the sequence's last token of the step
+  const int t_begin = blockIdx.y * kStateTile, t_end = min(t_begin + kStateTile, a.tokens);
   const float bias = a.bias != nullptr ? a.bias[c] : 0.f;
-  float* st = a.state + static_cast<size_t>(a.state_slot[seq]) * a.slot_stride;
   const int keep = a.taps - 1;
-  float u[kMaxTaps];
-  int first = -1;
-  for (int back = 0; back < keep; ++back) {
-    const int s = t - back;
-    if (first < 0 && s >= 0 && a.seq_of_token[s] == seq) {
-      u[back] = to_float(x[static_cast<size_t>(s) * a.ld_x + a.col_x + c]) + bias;
-    } else {
-      if (first < 0) first = s + 1;
-      u[back] = st[static_cast<size_t>(keep + (s - first)) * a.channels + c];
-    }
+  for (int t = t_begin; t < t_end; ++t) {
+    const int seq = a.seq_of_token[t];
+    if (t + 1 < a.tokens && a.seq_of_token[t + 1] == seq) continue;    // not the sequence's last token of the step
+    float* st = a.state + static_cast<size_t>(a.state_slot[seq]) * a.slot_stride;
+    const int first = conv_first(a.seq_of_token, t, seq, keep);
+    float u[kMaxTaps];
+#pragma unroll
+    for (int back = 0; back < kMaxTaps; ++back)
+      if (back < keep) u[back] = conv_input(a, x, st, t - back, first, c, bias);
+#pragma unroll
+    for (int back = 0; back < kMaxTaps; ++back)
+      if (back < keep) st[static_cast<size_t>(keep - 1 - back) * a.channels + c] = u[back];
   }
-  for (int back = 0; back < keep; ++back) st[static_cast<size_t>(keep - 1 - back) * a.channels + c] = u[back];
 }
 
 }  // namespace rl
@@ -238,13 +280,13 @@ int rl_streams_step(float* streams, const float* init, const void* y, int ld_y, 
 
 int rl_pair_norm_mean(int act_dtype, const void* a, int ld_a, const void* wa, float ca, const void* b, int ld_b,
                       const void* wb, float cb, int w_dtype, void* out, int ld_out, int tokens, int width, float eps,
-                      cudaStream_t stream) {
+                      const float* bias_a, const float* bias_b, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const int th = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
 #define RL_CASE(TA, TW)                                                                                       \
   launch_kernel(pair_norm_mean_kernel<TA, TW>, dim3(tokens), dim3(th), 0, stream, static_cast<const TA*>(a),  \
                 ld_a, static_cast<const TW*>(wa), ca, static_cast<const TA*>(b), ld_b,                        \
-                static_cast<const TW*>(wb), cb, static_cast<TA*>(out), ld_out, width, eps)
+                static_cast<const TW*>(wb), cb, static_cast<TA*>(out), ld_out, width, eps, bias_a, bias_b)
   if (act_dtype == RL_F32) RL_CASE(float, float);
   else if (w_dtype == RL_F32) RL_CASE(bf16, float);
   else RL_CASE(bf16, bf16);
@@ -262,12 +304,13 @@ int rl_short_conv(int act_dtype, const void* x, int ld_x, int col_x, const void*
   a.tokens = tokens; a.bias = bias; a.seq_of_token = seq_of_token; a.state_slot = state_slot; a.state = state;
   a.slot_stride = slot_stride;
   const int th = 128;
-  const dim3 grid((channels + th - 1) / th, tokens);
+  const dim3 grid((channels + th - 1) / th, (tokens + kConvTile - 1) / kConvTile);
+  const dim3 grid_state((channels + th - 1) / th, (tokens + kStateTile - 1) / kStateTile);
 #define RL_CASE(TA, TW)                                                                                        \
   do {                                                                                                         \
     launch_kernel(short_conv_kernel<TA, TW>, grid, dim3(th), 0, stream, a, static_cast<const TA*>(x),          \
                   static_cast<const TW*>(w), static_cast<TA*>(y));                                             \
-    if (taps > 1) launch_kernel(short_conv_state_kernel<TA>, grid, dim3(th), 0, stream, a, static_cast<const TA*>(x)); \
+    if (taps > 1) launch_kernel(short_conv_state_kernel<TA>, grid_state, dim3(th), 0, stream, a, static_cast<const TA*>(x)); \
   } while (0)
   if (act_dtype == RL_F32) RL_CASE(float, float);
   else if (w_dtype == RL_F32) RL_CASE(bf16, float);

@@ -945,17 +945,22 @@ def streams_step(streams: torch.Tensor, tokens: int, init: Optional[torch.Tensor
 
 
 def pair_norm_mean(a: torch.Tensor, wa: torch.Tensor, ca: float, b: torch.Tensor, wb: torch.Tensor, cb: float,
-                   out: torch.Tensor, eps: float, rows: Optional[int] = None) -> None:
-    """out = ca * rmsnorm(a) * wa + cb * rmsnorm(b) * wb over rows of the activation type (csrc/stream_ops.cu)."""
-    _need_cuda(a, b, wa, wb, out)
+                   out: torch.Tensor, eps: float, rows: Optional[int] = None, bias_a: Optional[torch.Tensor] = None,
+                   bias_b: Optional[torch.Tensor] = None) -> None:
+    """out = ca * rmsnorm(a + bias_a) * wa + cb * rmsnorm(b + bias_b) * wb over rows of the activation type; the
+    biases (float32 [width]) are optional (csrc/stream_ops.cu)."""
+    _need_cuda(a, b, wa, wb, out, bias_a, bias_b)
+    for bias in (bias_a, bias_b):
+        if bias is not None and (bias.dtype != torch.float32 or bias.numel() != a.shape[1] or not bias.is_contiguous()):
+            raise KernelError("pair_norm_mean: a bias is contiguous float32 [width]")
     if a.dtype != b.dtype or a.dtype != out.dtype or wa.dtype != wb.dtype or a.shape[1] != b.shape[1] \
             or a.stride(1) != 1 or b.stride(1) != 1 or out.stride(1) != 1 or wa.numel() != a.shape[1]:
         raise KernelError("pair_norm_mean: two inputs and an output of one type and width, weights of one type")
     f = _fn(_so(), "rl_pair_norm_mean", [c_int, c_void_p, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p, c_float,
-                                         c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p])
+                                         c_int, c_void_p, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p])
     _check(f(_code(a.dtype), _ptr(a), a.stride(0), _ptr(wa), float(ca), _ptr(b), b.stride(0), _ptr(wb), float(cb),
              _code(wa.dtype), _ptr(out), out.stride(0), rows if rows is not None else a.shape[0], a.shape[1],
-             float(eps), _stream()), "pair_norm_mean")
+             float(eps), _ptr(bias_a), _ptr(bias_b), _stream()), "pair_norm_mean")
 
 
 def short_conv(x: torch.Tensor, col_x: int, w: torch.Tensor, bias: Optional[torch.Tensor], y: torch.Tensor, col_y: int,

@@ -8,8 +8,8 @@ sum.  A side is any mixer that has ``inner_size()``, ``forward_inner(x, ctx, cac
 engine that side's ``cache_spec`` / ``state_spec`` (if both keep a state, a tuple of the two).  Tensor names
 of the pair are the sides' own with ``left.`` / ``right.`` in front (``parallel_spec`` builds the ``PartSpec``).
 
-``combine`` "normed": every side keeps its own output projection (with its bias, if it has one), each
-result is RMS-normed over the model width with a weight of the pair (``left.out`` / ``right.out``), and the
+``combine`` "normed": every side keeps its own output projection (with its bias, if it has one, added in
+float32 by the kernel that norms), each result is RMS-normed over the model width with a weight of the pair (``left.out`` / ``right.out``), and the
 pair's output is left_scale * N(left) + right_scale * N(right) (one kernel, csrc/stream_ops.cu).
 """
 
@@ -66,6 +66,8 @@ class ParallelMixers(Mixer):
             raise ValueError("a mixer that runs beside another one keeps at most one state")
         if p.combine not in ("sum", "normed"):
             raise ValueError(f"parallel_mixers: combine '{p.combine}' is not known (sum, normed)")
+        if p.combine == "sum" and any(getattr(m.params, "out_bias", False) for m in self.sides):
+            raise ValueError("parallel_mixers: a bias on a side's output projection needs combine 'normed'")
         self.widths = [m.inner_size() for m in self.sides]
         self.both_states = all(m.state_spec() is not None for m in self.sides)
 
@@ -126,7 +128,7 @@ class ParallelMixers(Mixer):
         y = rt.workspace.get("parallel.y", (rt.max_tokens, sum(self.widths)), rt.dtype)[:T]
         normed = p.combine == "normed"
         col = 0
-        outs = []
+        outs, biases = [], []
         for i, (m, width, scale) in enumerate(zip(self.sides, self.widths, self.scales)):
             heads = y[:, col:col + width]
             m.forward_inner(x, ctx, cache if m.cache_spec() is not None else None, self._state_of(i, state), heads,
@@ -135,15 +137,13 @@ class ParallelMixers(Mixer):
             if normed:         # the side's own output projection
                 o = rt.workspace.get(f"parallel.out{i}", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
                 linear(heads, m.out_weight(), o)
-                bias = m.out_bias() if hasattr(m, "out_bias") else None
-                if bias is not None:
-                    kernels.bias_act(o, bias, kernels.ACT_NONE)
                 op_mark(ctx, "o_proj", m.out_weight(), T)
                 outs.append(o)
+                biases.append(m.out_bias() if hasattr(m, "out_bias") else None)   # added in the norm's kernel
         out = rt.workspace.get("mixer.out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
         if normed:
             kernels.pair_norm_mean(outs[0], self.out_norms[0], self.scales[0], outs[1], self.out_norms[1],
-                                   self.scales[1], out, p.eps, rows=T)
+                                   self.scales[1], out, p.eps, rows=T, bias_a=biases[0], bias_b=biases[1])
             op_mark(ctx, "pair_norm+mean", nbytes=3.0 * T * p.hidden_size * out.element_size())
             return out
         linear(y, self.w_o, out)

@@ -8,10 +8,10 @@
 //
 // S is [D, DV] per (request, head) in float32, in the request's state slot: zero for a new request,
 // carried from step to step.  Columns of S never mix, so a CTA owns a few columns of one (sequence, head)
-// and walks the sequence's tokens in order; within a warp 32 / G columns x G groups of rows (G = 4, or 8 from
-// key size 128 on: shorter chains per token and more CTAs): a thread keeps D / G neighbouring rows of its
-// column in registers, sums its part of the two inner products in four independent chains, and shuffles
-// finish them.  q, k and the decays of a few tokens at a time are staged in shared memory by asynchronous
+// and walks the sequence's tokens in order; within a warp 32 / G columns x G groups of rows (long sequences: G = 4,
+// 8 from key size 64 and 16 from 128 on; steps of single tokens: G = 4): a thread keeps D / G neighbouring rows of its
+// column in registers.  With R = diag(a_t) S the read-out is o_t = R^T q_t + d (k_t . q_t), so a thread sums its
+// part of R^T k, R^T q and k . q in one pass over its rows and one round of shuffles finishes all three.  q, k and the decays of a few tokens at a time are staged in shared memory by asynchronous
 // copies into one of two buffers while the tokens of the other are worked on.  Everything here is float32:
 // q and k arrive as unit vectors, beta and the decays as numbers in (0, 1) (delta_prep_kernel makes them
 // from the projections); v is read in the activation type.
@@ -30,24 +30,13 @@
 namespace rl {
 
 constexpr int kD = RL_DELTA_DIM;
-constexpr int kGroups = kD >= 128 ? 8 : 4;         // groups of rows a column is split into
-constexpr int kRows = ((kD + kGroups - 1) / kGroups + 3) / 4 * 4;  // rows a thread keeps (a multiple of 4: float4 loads)
-constexpr int kDP = kRows * kGroups;               // D rounded up; the rows beyond D stay zero
-constexpr int kStride = kRows + 4;                 // floats from one group's rows to the next in shared memory (spreads the banks)
-constexpr int kSm = kGroups * kStride;             // floats of one staged vector
-constexpr int kWarpCols = 32 / kGroups;            // columns of a warp
-constexpr int kCols = 4 * kWarpCols;               // columns of a CTA (4 warps)
-constexpr int kTok = kD > 128 ? 4 : 8;             // tokens staged at a time (two such buffers)
+// Row groups a column is split into: many where sequences are long (a token's work is a chain that more
+// groups shorten), few where a step is mostly state traffic (single tokens: a warp then covers 8 neighbouring
+// columns of every row it loads and stores).
+constexpr int kGroupsLong = kD >= 128 ? 16 : (kD >= 64 ? 8 : 4);
+constexpr int kGroupsShort = kD > 128 ? 8 : 4;
 constexpr int kThreads = 128;
-constexpr int kVPer = (kTok * kCols + kThreads - 1) / kThreads;   // values a thread fetches per staged batch
 constexpr bool kVec = kD % 4 == 0;                 // rows of q, k and the decays start on 16-byte boundaries
-
-// Sum over the lanes that hold the groups of one column (lanes c, c + kWarpCols, c + 2 kWarpCols, ...).
-__device__ __forceinline__ float column_sum(float v) {
-#pragma unroll
-  for (int off = kWarpCols; off < 32; off <<= 1) v += __shfl_xor_sync(0xffffffffu, v, off);
-  return v;
-}
 
 __device__ __forceinline__ void async_copy4(float* dst, const float* src) {
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(static_cast<unsigned>(__cvta_generic_to_shared(dst))), "l"(src));
@@ -83,18 +72,26 @@ struct DeltaArgs {
   float* out;              // [tokens, heads * DV]
   int tokens, heads, qk_heads, dv;
   int vec_ok;              // q, k and decay are 16-byte aligned
+  int v_ok;                // pairs of values start on 4-byte boundaries
 };
 
 // Row r of a staged vector lies at (r / kRows) * kStride + r % kRows: a thread's rows are contiguous.
-template <typename T>
+template <typename T, int kGroups>
 __global__ void __launch_bounds__(kThreads)
 delta_rule_kernel(const DeltaArgs<T> a) {
+  constexpr int kRows = ((kD + kGroups - 1) / kGroups + 3) / 4 * 4;  // rows a thread keeps (a multiple of 4: float4 loads)
+  constexpr int kDP = kRows * kGroups;               // D rounded up; the rows beyond D stay zero
+  constexpr int kStride = kRows + 4;                 // floats from one group's rows to the next in shared memory (spreads the banks)
+  constexpr int kSm = kGroups * kStride;             // floats of one staged vector
+  constexpr int kWarpCols = 32 / kGroups;            // columns of a warp
+  constexpr int kCols = 4 * kWarpCols;               // columns of a CTA (4 warps)
+  constexpr int kTok = kD > 128 ? 4 : 8;             // tokens staged at a time (two such buffers)
   pdl_launch();
   pdl_wait();
   __shared__ __align__(16) float qs[2][kTok][kSm];
   __shared__ __align__(16) float ks[2][kTok][kSm];
   __shared__ __align__(16) float as[2][kTok][kSm];
-  __shared__ float vs[2][kTok][kCols];
+  __shared__ __align__(16) T vs[2][kTok][kCols];
   __shared__ float bs[2][kTok];
   const int seq = blockIdx.z, head = blockIdx.y;
   const int qk_head = head / (a.heads / a.qk_heads);
@@ -145,32 +142,27 @@ delta_rule_kernel(const DeltaArgs<T> a) {
         async_copy4(&as[b][tt][sm], a.decay + (t * a.heads + head) * kD + e);
       }
     }
-  };
-  // the values and betas of a batch pass through registers (the values arrive in the activation type)
-  float vreg[kVPer], breg = 0.f;
-  auto fetch = [&](int tb, int nt) {
-#pragma unroll
-    for (int j = 0; j < kVPer; ++j) {
-      const int i = threadIdx.x + j * kThreads;
-      const int tt = i / kCols, c = i - tt * kCols;
-      const int gc = blockIdx.x * kCols + c;
-      vreg[j] = (tt < nt && gc < a.dv) ? to_float(a.v[static_cast<size_t>(tb + tt) * a.ld_v + head * a.dv + gc]) : 0.f;
+    // the values of this CTA's columns (as they are, in the activation type) and the betas
+    const int col0 = blockIdx.x * kCols;
+    if (a.v_ok) {
+      constexpr int per_word = 4 / sizeof(T), words = kCols / per_word;       // 4-byte words of a token's values
+      for (int i = threadIdx.x; i < nt * words; i += kThreads) {
+        const int tt = i / words, c = (i - tt * words) * per_word;
+        if (col0 + c < a.dv)
+          async_copy4(reinterpret_cast<float*>(&vs[b][tt][c]),
+                      reinterpret_cast<const float*>(a.v + static_cast<size_t>(tb + tt) * a.ld_v + head * a.dv + col0 + c));
+      }
+    } else {
+      for (int i = threadIdx.x; i < nt * kCols; i += kThreads) {
+        const int tt = i / kCols, c = i - tt * kCols;
+        if (col0 + c < a.dv) vs[b][tt][c] = a.v[static_cast<size_t>(tb + tt) * a.ld_v + head * a.dv + col0 + c];
+      }
     }
-    if (threadIdx.x < nt) breg = a.beta[static_cast<size_t>(tb + threadIdx.x) * a.heads + head];
-  };
-  auto put = [&](int b) {
-#pragma unroll
-    for (int j = 0; j < kVPer; ++j) {
-      const int i = threadIdx.x + j * kThreads;
-      if (i < kTok * kCols) (&vs[b][0][0])[i] = vreg[j];
-    }
-    if (threadIdx.x < kTok) bs[b][threadIdx.x] = breg;
+    if (threadIdx.x < nt) async_copy4(&bs[b][threadIdx.x], a.beta + static_cast<size_t>(tb + threadIdx.x) * a.heads + head);
   };
   {
     const int nt = min(kTok, t1 - t0);
     stage(0, t0, nt);
-    fetch(t0, nt);
-    put(0);
     async_copies_done();
     __syncthreads();
   }
@@ -178,40 +170,42 @@ delta_rule_kernel(const DeltaArgs<T> a) {
   for (int tb = t0; tb < t1; tb += kTok, b ^= 1) {
     const int nt = min(kTok, t1 - tb);
     const int nn = min(kTok, t1 - tb - kTok);        // tokens of the batch after this one
-    if (nn > 0) {
-      stage(b ^ 1, tb + kTok, nn);
-      fetch(tb + kTok, nn);
-    }
-    for (int tt = 0; tt < nt; ++tt) {
+    if (nn > 0) stage(b ^ 1, tb + kTok, nn);
+    auto token = [&](int tt) {
+      // With R = diag(a) S:  d = beta (v - R^T k),  S = R + k d^T,  o = S^T q = R^T q + d (k . q): the three inner
+      // products over the rows are summed in one pass and finished by one round of shuffles.
       const float4* a4 = reinterpret_cast<const float4*>(&as[b][tt][group * kStride]);
       const float4* k4 = reinterpret_cast<const float4*>(&ks[b][tt][group * kStride]);
       const float4* q4 = reinterpret_cast<const float4*>(&qs[b][tt][group * kStride]);
       float kk[kRows];
-      float p0 = 0.f, p1 = 0.f, p2 = 0.f, p3 = 0.f;     // independent chains
+      float rk0 = 0.f, rk1 = 0.f, rq0 = 0.f, rq1 = 0.f, kq0 = 0.f, kq1 = 0.f;     // two chains each
 #pragma unroll
       for (int i = 0; i < kRows; i += 4) {
-        const float4 av = a4[i >> 2], kv = k4[i >> 2];
+        const float4 av = a4[i >> 2], kv = k4[i >> 2], qv = q4[i >> 2];
         kk[i] = kv.x; kk[i + 1] = kv.y; kk[i + 2] = kv.z; kk[i + 3] = kv.w;
-        S[i] *= av.x;     p0 = fmaf(S[i], kv.x, p0);
-        S[i + 1] *= av.y; p1 = fmaf(S[i + 1], kv.y, p1);
-        S[i + 2] *= av.z; p2 = fmaf(S[i + 2], kv.z, p2);
-        S[i + 3] *= av.w; p3 = fmaf(S[i + 3], kv.w, p3);
+        S[i] *= av.x;     rk0 = fmaf(S[i], kv.x, rk0);     rq0 = fmaf(S[i], qv.x, rq0);     kq0 = fmaf(kv.x, qv.x, kq0);
+        S[i + 1] *= av.y; rk1 = fmaf(S[i + 1], kv.y, rk1); rq1 = fmaf(S[i + 1], qv.y, rq1); kq1 = fmaf(kv.y, qv.y, kq1);
+        S[i + 2] *= av.z; rk0 = fmaf(S[i + 2], kv.z, rk0); rq0 = fmaf(S[i + 2], qv.z, rq0); kq0 = fmaf(kv.z, qv.z, kq0);
+        S[i + 3] *= av.w; rk1 = fmaf(S[i + 3], kv.w, rk1); rq1 = fmaf(S[i + 3], qv.w, rq1); kq1 = fmaf(kv.w, qv.w, kq1);
       }
-      const float sk = column_sum((p0 + p1) + (p2 + p3));
-      const float d = bs[b][tt] * (vs[b][tt][local_col] - sk);
-      p0 = p1 = p2 = p3 = 0.f;
+      float rk = rk0 + rk1, rq = rq0 + rq1, kq = kq0 + kq1;
 #pragma unroll
-      for (int i = 0; i < kRows; i += 4) {
-        const float4 qv = q4[i >> 2];
-        S[i] = fmaf(kk[i], d, S[i]);             p0 = fmaf(S[i], qv.x, p0);
-        S[i + 1] = fmaf(kk[i + 1], d, S[i + 1]); p1 = fmaf(S[i + 1], qv.y, p1);
-        S[i + 2] = fmaf(kk[i + 2], d, S[i + 2]); p2 = fmaf(S[i + 2], qv.z, p2);
-        S[i + 3] = fmaf(kk[i + 3], d, S[i + 3]); p3 = fmaf(S[i + 3], qv.w, p3);
+      for (int off = kWarpCols; off < 32; off <<= 1) {
+        rk += __shfl_xor_sync(0xffffffffu, rk, off);
+        rq += __shfl_xor_sync(0xffffffffu, rq, off);
+        kq += __shfl_xor_sync(0xffffffffu, kq, off);
       }
-      const float o = column_sum((p0 + p1) + (p2 + p3));
-      if (mine && group == 0) a.out[(static_cast<size_t>(tb + tt) * a.heads + head) * a.dv + col] = o;
+      const float d = bs[b][tt] * (to_float(vs[b][tt][local_col]) - rk);
+#pragma unroll
+      for (int i = 0; i < kRows; ++i) S[i] = fmaf(kk[i], d, S[i]);
+      if (mine && group == 0) a.out[(static_cast<size_t>(tb + tt) * a.heads + head) * a.dv + col] = fmaf(d, kq, rq);
+    };
+    if (nt == kTok) {          // a full batch, unrolled: the next token's loads are asked for while this one's sums are finished
+#pragma unroll
+      for (int tt = 0; tt < kTok; ++tt) token(tt);
+    } else {
+      for (int tt = 0; tt < nt; ++tt) token(tt);
     }
-    if (nn > 0) put(b ^ 1);
     async_copies_done();
     __syncthreads();
   }
@@ -327,7 +321,10 @@ int rl_delta_rule(int act_dtype, const float* q, const float* k, const void* v, 
                   long long slot_stride, float* out, int tokens, int sequences, int heads, int qk_heads, int dv,
                   cudaStream_t stream) {
   if (tokens <= 0 || sequences <= 0) return 0;
-  const dim3 grid((dv + kCols - 1) / kCols, heads, sequences);
+  // long sequences: many row groups; steps of (mostly) single tokens: few
+  const bool long_seqs = tokens >= 16 * sequences;
+  const int cols = 4 * (32 / (long_seqs ? kGroupsLong : kGroupsShort));
+  const dim3 grid((dv + cols - 1) / cols, heads, sequences);
 #define RL_CASE(T)                                                                                               \
   do {                                                                                                           \
     DeltaArgs<T> a;                                                                                              \
@@ -336,7 +333,9 @@ int rl_delta_rule(int act_dtype, const float* q, const float* k, const void* v, 
     a.out = out; a.tokens = tokens; a.heads = heads; a.qk_heads = qk_heads; a.dv = dv;                           \
     a.vec_ok = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |                               \
                  reinterpret_cast<uintptr_t>(decay)) & 15) == 0;                                                 \
-    launch_kernel(delta_rule_kernel<T>, grid, dim3(kThreads), 0, stream, a);                                          \
+    a.v_ok = sizeof(T) == 4 || ((reinterpret_cast<uintptr_t>(v) & 3) == 0 && ld_v % 2 == 0 && dv % 2 == 0);     \
+    if (long_seqs) launch_kernel(delta_rule_kernel<T, kGroupsLong>, grid, dim3(kThreads), 0, stream, a);         \
+    else launch_kernel(delta_rule_kernel<T, kGroupsShort>, grid, dim3(kThreads), 0, stream, a);                                          \
   } while (0)
   if (act_dtype == RL_F32) RL_CASE(float);
   else RL_CASE(bf16);

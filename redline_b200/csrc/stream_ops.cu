@@ -12,13 +12,14 @@
 // pair_norm_mean_kernel, one CTA per token: out = ca * N(a + bias_a, wa) + cb * N(b + bias_b, wb), N the RMS
 // norm, the biases (float32, of the two products that made a and b) optional.
 //
-// short_conv_kernel, one thread per channel and eight tokens: y_t = act(sum_j w[c, j] (u_(t - taps + 1 + j) + bias_c)),
+// short_conv_kernel, one thread per channel and token (eight tokens in a large step): y_t = act(sum_j w[c, j] (u_(t - taps + 1 + j) + bias_c)),
 // over the tokens of the token's own sequence; tokens before the step's portion come from the request's state
 // slot, which holds the last taps - 1 inputs (bias added) in float32: [taps - 1, channels], the oldest first,
 // zeros for a new request.  short_conv_state_kernel then moves the slot on: the thread of a sequence's last
 // token gathers the channel's last taps - 1 inputs (from the step, or from the old slot where the portion
 // is shorter) and writes them back.  The two are separate launches because the first tokens of a portion
-// read what the last one replaces.
+// read what the last one replaces; in a step where every sequence has one token the first kernel moves the
+// slot on itself.
 #include "common.cuh"
 
 namespace rl {
@@ -146,6 +147,8 @@ __global__ void pair_norm_mean_kernel(const TA* __restrict__ a, int ld_a, const 
 
 struct ConvArgs {
   int ld_x, col_x, ld_y, col_y, channels, taps, act, tokens;
+  int tile;                      // consecutive tokens a thread of short_conv_kernel walks
+  int own_state;                 // every sequence has one token in this step: the thread of the token moves the slot on itself
   const float* bias;             // [channels] or null
   const int32_t* seq_of_token;
   const int32_t* state_slot;
@@ -153,7 +156,7 @@ struct ConvArgs {
   long long slot_stride;
 };
 
-constexpr int kConvTile = 8;         // tokens a thread of short_conv_kernel walks
+constexpr int kConvTile = 8;         // tokens a thread of short_conv_kernel walks in a step of many tokens (one in a small step)
 constexpr int kStateTile = 32;       // tokens a thread of short_conv_state_kernel looks at
 
 // Input u_s of channel c for the token at index s of the step, or, where s lies before the first token of
@@ -173,7 +176,7 @@ __device__ __forceinline__ int conv_first(const int32_t* __restrict__ seq_of_tok
   return first;
 }
 
-// One thread per channel and kConvTile consecutive tokens: the window of the last taps - 1 inputs slides in
+// One thread per channel and a.tile consecutive tokens: the window of the last taps - 1 inputs slides in
 // registers from token to token and is gathered anew where another sequence begins.
 template <typename TA, typename TW>
 __global__ void short_conv_kernel(const ConvArgs a, const TA* __restrict__ x, const TW* __restrict__ w,
@@ -182,7 +185,7 @@ __global__ void short_conv_kernel(const ConvArgs a, const TA* __restrict__ x, co
   pdl_wait();
   const int c = blockIdx.x * blockDim.x + threadIdx.x;
   if (c >= a.channels) return;
-  const int t_begin = blockIdx.y * kConvTile, t_end = min(t_begin + kConvTile, a.tokens);
+  const int t_begin = blockIdx.y * a.tile, t_end = min(t_begin + a.tile, a.tokens);
   const float bias = a.bias != nullptr ? a.bias[c] : 0.f;
   const int keep = a.taps - 1;
   float wt[kMaxTaps], win[kMaxTaps];     // win[j]: the input j + 1 tokens back, wt[j] its weight
@@ -212,6 +215,13 @@ __global__ void short_conv_kernel(const ConvArgs a, const TA* __restrict__ x, co
 #pragma unroll
     for (int j = kMaxTaps - 1; j > 0; --j) win[j] = win[j - 1];
     win[0] = u;
+    if (a.own_state) {                   // nobody else reads this sequence's slot in this step
+      float* st = a.state + static_cast<size_t>(a.state_slot[seq]) * a.slot_stride;
+#pragma unroll
+      for (int j = 0; j < kMaxTaps; ++j)
+        if (j < keep) st[static_cast<size_t>(keep - 1 - j) * a.channels + c] = win[j];
+      seq = -1;                          // (the next token gathers its own window)
+    }
     if (a.act == ACT_SILU) acc = acc / (1.f + expf(-acc));
     y[static_cast<size_t>(t) * a.ld_y + a.col_y + c] = from_float<TA>(acc);
   }
@@ -296,21 +306,25 @@ int rl_pair_norm_mean(int act_dtype, const void* a, int ld_a, const void* wa, fl
 
 int rl_short_conv(int act_dtype, const void* x, int ld_x, int col_x, const void* w, int w_dtype, const float* bias,
                   void* y, int ld_y, int col_y, int channels, int taps, int act, const int32_t* seq_of_token,
-                  const int32_t* state_slot, float* state, long long slot_stride, int tokens, cudaStream_t stream) {
+                  const int32_t* state_slot, float* state, long long slot_stride, int tokens, int single,
+                  cudaStream_t stream) {
   if (tokens <= 0 || channels <= 0) return 0;
   if (taps < 1 || taps > kMaxTaps) return static_cast<int>(cudaErrorInvalidValue);
   ConvArgs a;
   a.ld_x = ld_x; a.col_x = col_x; a.ld_y = ld_y; a.col_y = col_y; a.channels = channels; a.taps = taps; a.act = act;
   a.tokens = tokens; a.bias = bias; a.seq_of_token = seq_of_token; a.state_slot = state_slot; a.state = state;
   a.slot_stride = slot_stride;
+  a.own_state = (single && taps > 1) ? 1 : 0;
   const int th = 128;
-  const dim3 grid((channels + th - 1) / th, (tokens + kConvTile - 1) / kConvTile);
+  // enough threads for the machine first: a thread walks several tokens only where there are thousands of them
+  a.tile = static_cast<long long>(channels) * tokens >= (1ll << 20) ? kConvTile : 1;
+  const dim3 grid((channels + th - 1) / th, (tokens + a.tile - 1) / a.tile);
   const dim3 grid_state((channels + th - 1) / th, (tokens + kStateTile - 1) / kStateTile);
 #define RL_CASE(TA, TW)                                                                                        \
   do {                                                                                                         \
     launch_kernel(short_conv_kernel<TA, TW>, grid, dim3(th), 0, stream, a, static_cast<const TA*>(x),          \
                   static_cast<const TW*>(w), static_cast<TA*>(y));                                             \
-    if (taps > 1) launch_kernel(short_conv_state_kernel<TA>, grid_state, dim3(th), 0, stream, a, static_cast<const TA*>(x)); \
+    if (taps > 1 && !single) launch_kernel(short_conv_state_kernel<TA>, grid_state, dim3(th), 0, stream, a, static_cast<const TA*>(x)); \
   } while (0)
   if (act_dtype == RL_F32) RL_CASE(float, float);
   else if (w_dtype == RL_F32) RL_CASE(bf16, float);

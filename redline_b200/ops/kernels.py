@@ -964,12 +964,14 @@ def pair_norm_mean(a: torch.Tensor, wa: torch.Tensor, ca: float, b: torch.Tensor
 
 
 def short_conv(x: torch.Tensor, col_x: int, w: torch.Tensor, bias: Optional[torch.Tensor], y: torch.Tensor, col_y: int,
-               act: int, seq_of_token: torch.Tensor, state_slot: torch.Tensor, state: torch.Tensor, tokens: int) -> None:
+               act: int, seq_of_token: torch.Tensor, state_slot: torch.Tensor, state: torch.Tensor, tokens: int,
+               single: bool = False) -> None:
     """Causal convolution over time on ``w.shape[0]`` channels of x's rows, from column ``col_x``, into y's from
     ``col_y`` (another buffer): y_t = act(sum_j w[c, j] (x_(t - taps + 1 + j) + bias_c)) within a token's own
     sequence; what lies before the step's portion comes from the sequence's slot of ``state`` (float32
     [slots, (taps - 1) * channels]: the last inputs, zeros for a new request), which is then moved on
-    (csrc/stream_ops.cu).  ``act``: ACT_NONE or ACT_SILU."""
+    (csrc/stream_ops.cu).  ``act``: ACT_NONE or ACT_SILU.  ``single``: every sequence of the step has exactly one
+    token (one launch instead of two)."""
     _need_cuda(x, w, bias, y, state)
     channels, taps = w.shape
     if x.dtype != y.dtype or x.stride(1) != 1 or y.stride(1) != 1 or not w.is_contiguous() \
@@ -980,10 +982,10 @@ def short_conv(x: torch.Tensor, col_x: int, w: torch.Tensor, bias: Optional[torc
     if bias is not None and (bias.dtype != torch.float32 or bias.numel() != channels or not bias.is_contiguous()):
         raise KernelError("short_conv: the bias is contiguous float32 [channels]")
     f = _fn(_so(), "rl_short_conv", [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
-                                     c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_void_p])
+                                     c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_longlong, c_int, c_int, c_void_p])
     _check(f(_code(x.dtype), _ptr(x), x.stride(0), col_x, _ptr(w), _code(w.dtype), _ptr(bias), _ptr(y), y.stride(0),
              col_y, channels, taps, act, _ptr(seq_of_token), _ptr(state_slot), _ptr(state), state.stride(0), tokens,
-             _stream()), "short_conv", 2 if taps > 1 else 1)
+             1 if single else 0, _stream()), "short_conv", 2 if (taps > 1 and not single) else 1)
 
 
 # ------------------------------------------------------------------- the gated delta rule

@@ -233,7 +233,7 @@ class MapsAttention(Mixer):
             if state is None:          # one tap: a weight per channel, nothing carried
                 state = ws.get("mattn.no_state", (rt.max_seqs + 1, 1), torch.float32)
             kernels.short_conv(qkv, 0, self.w_conv, self.b_qkv, conv, 0, kernels.ACT_NONE, ctx.seq_of_token,
-                               ctx.state_slot, state, T)
+                               ctx.state_slot, state, T, single=ctx.num_decode == ctx.S == T)
             qkv = conv
         elif self.b_qkv is not None:
             kernels.bias_act(qkv, self.b_qkv, kernels.ACT_NONE, cols=self.qkv_size)

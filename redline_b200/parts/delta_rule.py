@@ -143,7 +143,7 @@ class GatedDelta(Mixer):
         if conv_state is None:           # one tap: a weight per channel and the activation
             conv_state = ws.get("delta.no_state", (rt.max_seqs + 1, 1), torch.float32)
         kernels.short_conv(proj, 0, self.w_conv, None, conv, 0, self.act, ctx.seq_of_token, ctx.state_slot,
-                           conv_state, T)
+                           conv_state, T, single=ctx.num_decode == ctx.S == T)
         op_mark(ctx, "conv+act", nbytes=2.0 * T * self.conv_size * proj.element_size())
         H, D = p.num_heads, p.dim
         zb = ws.get("delta.zb", (rt.max_tokens, H), torch.float32)[:T]

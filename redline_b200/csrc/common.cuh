@@ -133,6 +133,22 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+// The same without the attribute: the kernel begins when its predecessor has completed, so its CTAs are
+// handed out over an empty machine (a small grid of long-running CTAs that begins while the predecessor drains
+// lands on the few SMs that happen to be free first, several CTAs on each, and runs that much longer).
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_kernel_serial(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                        cudaStream_t stream, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cfg.attrs = nullptr;
+  cfg.numAttrs = 0;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+
 }  // namespace rl
 
 #define RL_LAUNCH_END() return static_cast<int>(cudaGetLastError())

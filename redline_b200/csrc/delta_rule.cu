@@ -321,7 +321,8 @@ int rl_delta_rule(int act_dtype, const float* q, const float* k, const void* v, 
                   long long slot_stride, float* out, int tokens, int sequences, int heads, int qk_heads, int dv,
                   cudaStream_t stream) {
   if (tokens <= 0 || sequences <= 0) return 0;
-  // long sequences: many row groups; steps of (mostly) single tokens: few
+  // long sequences: many row groups, and a launch that waits for an empty machine (few CTAs that run long: begun
+  // while the kernel before drains, they would share a few SMs); steps of (mostly) single tokens: few row groups
   const bool long_seqs = tokens >= 16 * sequences;
   const int cols = 4 * (32 / (long_seqs ? kGroupsLong : kGroupsShort));
   const dim3 grid((dv + cols - 1) / cols, heads, sequences);
@@ -334,7 +335,7 @@ int rl_delta_rule(int act_dtype, const float* q, const float* k, const void* v, 
     a.vec_ok = ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) |                               \
                  reinterpret_cast<uintptr_t>(decay)) & 15) == 0;                                                 \
     a.v_ok = sizeof(T) == 4 || ((reinterpret_cast<uintptr_t>(v) & 3) == 0 && ld_v % 2 == 0 && dv % 2 == 0);     \
-    if (long_seqs) launch_kernel(delta_rule_kernel<T, kGroupsLong>, grid, dim3(kThreads), 0, stream, a);         \
+    if (long_seqs) launch_kernel_serial(delta_rule_kernel<T, kGroupsLong>, grid, dim3(kThreads), 0, stream, a);  \
     else launch_kernel(delta_rule_kernel<T, kGroupsShort>, grid, dim3(kThreads), 0, stream, a);                                          \
   } while (0)
   if (act_dtype == RL_F32) RL_CASE(float);

@@ -11,7 +11,7 @@
 // and walks the sequence's tokens in order; within a warp 32 / G columns x G groups of rows (long sequences: G = 4,
 // 8 from key size 64 and 16 from 128 on; steps of single tokens: G = 4): a thread keeps D / G neighbouring rows of its
 // column in registers.  With R = diag(a_t) S the read-out is o_t = R^T q_t + d (k_t . q_t), so a thread sums its
-// part of R^T k, R^T q and k . q in one pass over its rows and one round of shuffles finishes all three.  q, k and the decays of a few tokens at a time are staged in shared memory by asynchronous
+// part of R^T k, R^T q and k . q in one pass over its rows and one shuffle reduction finishes all three.  q, k and the decays of a few tokens at a time are staged in shared memory by asynchronous
 // copies into one of two buffers while the tokens of the other are worked on.  Everything here is float32:
 // q and k arrive as unit vectors, beta and the decays as numbers in (0, 1) (delta_prep_kernel makes them
 // from the projections); v is read in the activation type.
@@ -173,7 +173,7 @@ delta_rule_kernel(const DeltaArgs<T> a) {
     if (nn > 0) stage(b ^ 1, tb + kTok, nn);
     auto token = [&](int tt) {
       // With R = diag(a) S:  d = beta (v - R^T k),  S = R + k d^T,  o = S^T q = R^T q + d (k . q): the three inner
-      // products over the rows are summed in one pass and finished by one round of shuffles.
+      // products over the rows are summed in one pass and finished by one shuffle reduction.
       const float4* a4 = reinterpret_cast<const float4*>(&as[b][tt][group * kStride]);
       const float4* k4 = reinterpret_cast<const float4*>(&ks[b][tt][group * kStride]);
       const float4* q4 = reinterpret_cast<const float4*>(&qs[b][tt][group * kStride]);

@@ -53,6 +53,9 @@ def plain_delta_from(S, q, k, v, beta, decay):
     (64, 40, 2, 1, (1, 1, 1), torch.bfloat16),            # single tokens
     (128, 72, 2, 2, (150, 9), torch.float32),             # 16 row groups over a long sequence, 4 over the mix
     (24, 16, 2, 2, (8, 16, 9), torch.float32),            # exactly one and two staged batches, and one token more
+    (256, 24, 1, 1, (40, 3), torch.float32),              # the largest key size: four tokens staged at a time
+    (256, 16, 2, 1, (80,), torch.bfloat16),
+    (48, 40, 6, 2, (5, 64, 2), torch.bfloat16),           # three heads to a q/k head
 ])
 def test_recurrence_from_states_in_shuffled_slots(D, DV, H, HQ, lengths, act):
     from redline_b200.ops import kernels

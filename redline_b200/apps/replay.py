@@ -29,10 +29,11 @@ class ReplaySession:
 
     def run_step(self, entries: Sequence[Dict[str, Any]], end: Sequence[Any]) -> Optional[np.ndarray]:
         """Runs one step; returns the float32 logits [wanted, vocab] or None if nothing was wanted."""
-        batch = [(e["id"], e.get("tokens", []), e.get("want", [])) for e in entries]
+        # (an entry without tokens brings nothing to run)
+        batch = [(e["id"], e["tokens"], e.get("want", [])) for e in entries if len(e.get("tokens", [])) > 0]
         wanted = sum(len(w) for _, _, w in batch)
         out = None
-        if any(len(t) for _, t, _ in batch):
+        if batch:
             logits = self.engine.step_tokens(batch)
             if wanted:
                 out = logits.cpu().numpy().astype("<f4", copy=False)

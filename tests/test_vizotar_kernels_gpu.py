@@ -221,7 +221,7 @@ def test_convolution_of_a_large_step():
 
 # ---------------------------------------------------------------------------- streams and pairs
 
-@pytest.mark.parametrize("n,width,dtype", [(1, 100, torch.float32), (4, 256, torch.bfloat16), (3, 1000, torch.float32),
+@pytest.mark.parametrize("n,width,dtype", [(1, 100, torch.float32), (4, 320, torch.bfloat16), (3, 1000, torch.float32),
                                            (8, 64, torch.bfloat16), (5, 4100, torch.float32)])
 def test_streams_boundary_in_all_its_modes(n, width, dtype):
     from redline_b200.ops import kernels

@@ -797,3 +797,220 @@ class VizotarConfig(ModelConfig):
         if self.eos_token_ids:
             out["eos_token_id"] = list(self.eos_token_ids)
         return out
+
+
+# ------------------------------------------------------------------------------------------------ Venezen
+
+@dataclass(frozen=True)
+class VenezenRotation:
+    base: float
+    dims: int                 # the first so many entries of the rotated part turn, entry i with i + dims / 2
+
+
+@dataclass(frozen=True)
+class VenezenLatent:
+    """A 'latent_attention' mixer: keys and values of all heads come from one cached latent vector per token."""
+
+    heads: int
+    dim: int                  # unrotated entries of a head's query and key
+    rot_dim: int              # rotated entries (the key's are one vector for all heads)
+    vdim: int
+    kv_rank: int              # size of the latent
+    scale: float
+    rot: VenezenRotation
+
+
+@dataclass(frozen=True)
+class VenezenWindowed:
+    """An 'attention' mixer: grouped heads over a sliding window, the keys serving as values."""
+
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    scale: float
+    window: int               # mask.size; 0: every earlier key
+
+
+@dataclass(frozen=True)
+class VenezenShared:
+    ff: int
+    limit: float
+
+
+@dataclass(frozen=True)
+class VenezenMLP:
+    kind: str                 # dense | moe
+    ff: int                   # dense: width of the layer; moe: of one expert
+    limit: float = 0.0        # moe: the clamp of an expert's gate and up
+    experts: int = 0
+    identity: int = 0         # router outputs behind the experts that stand for the input itself
+    top: int = 0
+    scale: float = 1.0        # factor on the chosen experts' weights
+    shared: Optional[VenezenShared] = None
+
+
+@dataclass(frozen=True)
+class VenezenLayer:
+    type: str                 # latent_attention | attention
+    mixer: Any
+    mlp: Optional[VenezenMLP]
+
+
+@dataclass(frozen=True)
+class VenezenLoop:
+    """Layers ``start`` .. ``stop`` - 1 run ``times`` times in a row on the same tensors."""
+
+    start: int
+    stop: int
+    times: int
+
+
+@dataclass(frozen=True)
+class VenezenConfig(ModelConfig):
+    """``Venezen``: pre-norm layers (layer norm with a weight) on one float32 stream fed by a scaled embedding.
+    Mixers: attention over a cached latent with a partly rotated key shared by all heads, or grouped attention
+    over a window whose keys are its values, with a distance bias per head and a one in the softmax's
+    denominator.  Feed-forwards: dense SiLU-gated with biases, or routed experts with clamped gate and up, a
+    choice corrected per expert, identity experts and a shared expert.  A run of layers may be repeated; the
+    head is the embedding table.  config.json lists the layers under ``layers``."""
+
+    norm_eps: float = 1e-6
+    embedding_scale: float = 1.0
+    layers: Tuple[VenezenLayer, ...] = ()
+    loop: Optional[VenezenLoop] = None
+
+    @classmethod
+    def from_hf(cls, cfg: Dict[str, Any], model_dir: Optional[str] = None) -> "VenezenConfig":
+        layers: List[VenezenLayer] = []
+        for i, entry in enumerate(_need(cfg, "layers")):
+            where = f"layers[{i}]"
+            kind = _need(entry, "type", where)
+            m = _need(entry, "mixer", where)
+            mw = where + ".mixer"
+            if kind == "latent_attention":
+                rot = _need(m, "rot", mw)
+                mixer: Any = VenezenLatent(
+                    heads=int(_need(m, "heads", mw)), dim=int(_need(m, "dim", mw)), rot_dim=int(_need(m, "rot_dim", mw)),
+                    vdim=int(_need(m, "vdim", mw)), kv_rank=int(_need(m, "kv_rank", mw)), scale=float(_need(m, "scale", mw)),
+                    rot=VenezenRotation(float(_need(rot, "base", mw + ".rot")), int(_need(rot, "dims", mw + ".rot"))))
+            elif kind == "attention":
+                heads = int(_need(m, "heads", mw))
+                mixer = VenezenWindowed(
+                    heads=heads, kv_heads=int(m.get("kv_heads") or heads), dim=int(_need(m, "dim", mw)),
+                    vdim=int(_need(m, "vdim", mw)), scale=float(_need(m, "scale", mw)),
+                    window=int((m.get("mask") or {}).get("size", 0)))
+            else:
+                raise ConfigError(f"{where}: mixer type '{kind}' is not supported (latent_attention, attention)")
+            mlp = entry.get("mlp")
+            ff: Optional[VenezenMLP] = None
+            if mlp is not None:
+                fw = where + ".mlp"
+                mk = _need(mlp, "kind", fw)
+                if mk == "dense":
+                    ff = VenezenMLP("dense", int(_need(mlp, "ff", fw)))
+                elif mk == "moe":
+                    r = _need(mlp, "router", fw)
+                    e = _need(mlp, "expert", fw)
+                    sh = mlp.get("shared")
+                    ff = VenezenMLP(
+                        "moe", int(_need(e, "ff", fw + ".expert")), limit=float(_need(e, "limit", fw + ".expert")),
+                        experts=int(_need(r, "experts", fw + ".router")), identity=int(r.get("identity") or 0),
+                        top=int(_need(r, "top", fw + ".router")), scale=float(r.get("scale", 1.0)),
+                        shared=VenezenShared(int(_need(sh, "ff", fw + ".shared")), float(_need(sh, "limit", fw + ".shared")))
+                        if sh else None)
+                else:
+                    raise ConfigError(f"{fw}: kind '{mk}' is not supported (dense, moe)")
+            layers.append(VenezenLayer(kind, mixer, ff))
+        lp = cfg.get("loop")
+        loop = None
+        if lp:
+            loop = VenezenLoop(int(_need(lp, "start", "loop")), int(_need(lp, "stop", "loop")), int(_need(lp, "times", "loop")))
+        eos = cfg.get("eos_token_id")
+        eos = [] if eos is None else ([eos] if isinstance(eos, int) else list(eos))
+        bos = cfg.get("bos_token_id")
+        c = cls(architecture="Venezen", vocab_size=int(_need(cfg, "vocab")), hidden_size=int(_need(cfg, "width")),
+                max_position_embeddings=int(cfg.get("max_positions", 1 << 30)),
+                bos_token_id=int(bos) if bos is not None else -1, eos_token_ids=tuple(int(e) for e in eos),
+                norm_eps=float(_need(_need(cfg, "norm"), "eps", "norm")),
+                embedding_scale=float((cfg.get("embedding") or {}).get("scale", 1.0)),
+                layers=tuple(layers), loop=loop)
+        c.validate()
+        return c
+
+    def validate(self) -> None:
+        if self.vocab_size <= 0 or self.hidden_size <= 0 or not self.layers:
+            raise ConfigError("vocab, width and the number of layers must be positive")
+        if not self.norm_eps > 0:
+            raise ConfigError(f"norm.eps must be positive, got {self.norm_eps}")
+        for i, layer in enumerate(self.layers):
+            m = layer.mixer
+            mw = f"layers[{i}].mixer"
+            if layer.type == "latent_attention":
+                if min(m.heads, m.dim, m.vdim, m.kv_rank) <= 0 or m.rot_dim < 0:
+                    raise ConfigError(f"{mw}: heads, dim, vdim and kv_rank must be positive")
+                if m.rot_dim > 0 and (m.rot.dims <= 0 or m.rot.dims % 2 != 0 or m.rot.dims > m.rot_dim or not m.rot.base > 0):
+                    raise ConfigError(f"{mw}: rot.dims must be even and at most rot_dim, rot.base positive")
+            else:
+                if m.heads <= 0 or m.kv_heads <= 0 or m.heads % m.kv_heads != 0 or m.dim <= 0:
+                    raise ConfigError(f"{mw}: heads must be a positive multiple of kv_heads, dim positive")
+                if m.vdim != m.dim:
+                    raise ConfigError(f"{mw}: the keys are the values, so vdim must equal dim")
+                if m.window < 0:
+                    raise ConfigError(f"{mw}: mask.size must not be negative")
+            f = layer.mlp
+            fw = f"layers[{i}].mlp"
+            if f is not None and f.ff <= 0:
+                raise ConfigError(f"{fw}: ff must be positive")
+            if f is not None and f.kind == "moe":
+                if f.experts < 0 or f.identity < 0 or not 1 <= f.top <= f.experts + f.identity or not f.limit > 0:
+                    raise ConfigError(f"{fw}: top must lie between 1 and experts + identity, limit be positive")
+                if f.shared is not None and (f.shared.ff <= 0 or not f.shared.limit > 0):
+                    raise ConfigError(f"{fw}.shared: ff and limit must be positive")
+        lp = self.loop
+        if lp is not None and not (0 <= lp.start < lp.stop <= len(self.layers) and lp.times >= 1):
+            raise ConfigError("loop: 0 <= start < stop <= number of layers, times at least 1")
+
+    def run_order(self) -> List[Tuple[int, bool]]:
+        """(layer, whether the embedding output is added to the stream right before it) in the order of a pass."""
+        n = len(self.layers)
+        lp = self.loop
+        if lp is None:
+            return [(i, False) for i in range(n)]
+        order = [(i, False) for i in range(lp.start)]
+        for rep in range(lp.times):
+            order += [(i, rep > 0 and i == lp.start) for i in range(lp.start, lp.stop)]
+        return order + [(i, False) for i in range(lp.stop, n)]
+
+    def to_hf(self) -> Dict[str, Any]:
+        layers = []
+        for layer in self.layers:
+            m = layer.mixer
+            if layer.type == "latent_attention":
+                mixer: Dict[str, Any] = {"heads": m.heads, "dim": m.dim, "rot_dim": m.rot_dim, "vdim": m.vdim,
+                                         "kv_rank": m.kv_rank, "scale": m.scale,
+                                         "rot": {"base": m.rot.base, "dims": m.rot.dims}}
+            else:
+                mixer = {"heads": m.heads, "kv_heads": m.kv_heads, "dim": m.dim, "vdim": m.vdim, "scale": m.scale,
+                         "mask": {"size": m.window}}
+            f = layer.mlp
+            if f is None:
+                mlp = None
+            elif f.kind == "dense":
+                mlp = {"kind": "dense", "ff": f.ff}
+            else:
+                mlp = {"kind": "moe", "expert": {"ff": f.ff, "limit": f.limit},
+                       "router": {"experts": f.experts, "identity": f.identity, "top": f.top, "scale": f.scale}}
+                if f.shared is not None:
+                    mlp["shared"] = {"ff": f.shared.ff, "limit": f.shared.limit}
+            layers.append({"type": layer.type, "mixer": mixer, "mlp": mlp})
+        out: Dict[str, Any] = {"architecture": "Venezen", "vocab": self.vocab_size, "width": self.hidden_size,
+                               "embedding": {"scale": self.embedding_scale}, "norm": {"eps": self.norm_eps},
+                               "layers": layers}
+        if self.loop is not None:
+            out["loop"] = {"start": self.loop.start, "stop": self.loop.stop, "times": self.loop.times}
+        if self.bos_token_id >= 0:
+            out["bos_token_id"] = self.bos_token_id
+        if self.eos_token_ids:
+            out["eos_token_id"] = list(self.eos_token_ids)
+        return out

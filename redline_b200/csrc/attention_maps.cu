@@ -10,13 +10,16 @@
 //   M = 1:  o_h = a_{h,0};          M = 2:  o_h = a_{h,0} - lambda * a_{h,1}
 //   sink:       a learned number per head joins the softmax's denominator, exp(sink_h) once, with no key and
 //               no value (M = 1)
+//   slopes:     a number per head times the distance is taken off the score, s_j <- s_j - slope_h * (i - j)
 //   unit_norm:  o_h <- o_h / sqrt(mean(o_h^2) + eps)
 //   o_h <- o_h * post_scale, and with a gate o_h <- o_h * sigmoid(gate), the gate one number per head
 //   (gate_mode 1: gate[token, h]) or per entry (gate_mode 2: gate[token, h * DV + d])
 //
 // Layouts: q [tokens, q_stride] with row (h, m) at column (h * M + m) * D; the key cache
 // [pages, G * M, page_size, D] (kv head g's map m is head g * M + m); the value cache
-// [pages, G, page_size, DV]; out [tokens, out_stride] with head h at column h * DV.
+// [pages, G, page_size, VS] of which a row's first DV entries are the value (VS = DV unless the module is
+// compiled with -DRL_V_STRIDE: a mixer whose values are the keys, or the leading part of them, hands the key
+// cache in as the value cache with VS = D); out [tokens, out_stride] with head h at column h * DV.
 //
 // Scores, softmax, the combination of the maps and the norm are float32 for both element types.
 // Single tokens: one CTA per (128-key partition, kv head, item) over absolute partitions, so a row's
@@ -34,7 +37,11 @@
 
 namespace rl {
 
-constexpr int kD = RL_QK_DIM, kDV = RL_V_DIM, kM = RL_MAPS;
+#ifndef RL_V_STRIDE
+#define RL_V_STRIDE RL_V_DIM
+#endif
+constexpr int kD = RL_QK_DIM, kDV = RL_V_DIM, kM = RL_MAPS, kVS = RL_V_STRIDE;
+static_assert(kVS >= kDV, "a value row holds the value");
 static_assert(kM == 1 || kM == 2, "one or two score maps");
 static_assert(kD >= 1 && kD <= 256 && kDV >= 1 && kDV <= 256, "sizes out of range");
 constexpr int kVQ = (kDV + 3) / 4;             // value columns of one of the four threads that share a query row
@@ -52,6 +59,7 @@ struct MaskArgs {
 template <typename T>
 struct TailArgs {
   const float* sink;     // [heads] or null
+  const float* slopes;   // [heads] or null: slope_h * (i - j) is taken off the score of key j for query i
   const T* gate;         // rows of gate_stride entries, or null
   int gate_stride, gate_mode;
 };
@@ -108,7 +116,7 @@ maps_decode_kernel(const MapsDecodeArgs<T> a) {
   constexpr int E = (kD % VEC == 0) ? VEC : 1;          // piece of a key
   constexpr int CH = kD / E;
   constexpr int CPL = (CH + kLPK - 1) / kLPK;
-  constexpr int EVV = (kDV % VEC == 0) ? VEC : 1;         // piece of a value row
+  constexpr int EVV = (kDV % VEC == 0 && kVS % VEC == 0) ? VEC : 1;         // piece of a value row
   constexpr int CHV = kDV / EVV;
   constexpr int CPLV = (CHV + kLPK - 1) / kLPK;
   __shared__ float qs[kRows][kD];
@@ -180,6 +188,7 @@ maps_decode_kernel(const MapsDecodeArgs<T> a) {
           v += __shfl_xor_sync(0xffffffffu, v, 4);
           if (lane8 == 0 && j < j_hi) {
             if (a.softcap > 0.f) v = a.softcap * tanhf(v * inv_cap);
+            if (a.tail.slopes != nullptr && g < ng) v -= a.tail.slopes[kvh * G + g0 + g] * static_cast<float>(me - j);
             sc[g][j - base] = live ? v : -INFINITY;
           }
         }
@@ -216,7 +225,7 @@ maps_decode_kernel(const MapsDecodeArgs<T> a) {
         const int j = base + it * kKeysPerIter + slot;
         if (j >= j_hi || !key_visible(j, me, a.mask)) continue;
         const size_t page = pages[it];
-        const T* vp = a.vcache + ((page * a.kv_heads + kvh) * a.page_size + j % a.page_size) * kDV;
+        const T* vp = a.vcache + ((page * a.kv_heads + kvh) * a.page_size + j % a.page_size) * kVS;
         float p[kRows];
 #pragma unroll
         for (int g = 0; g < kRows; ++g) p[g] = g < ng ? sc[g][j - base] : 0.f;
@@ -371,6 +380,7 @@ maps_prefill_kernel(const MapsPrefillArgs<T> a) {
   const int my_pos = pos0 + r;
   const int k_end = pos0 + rows;     // exclusive
   const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
+  const float slope = a.tail.slopes != nullptr ? a.tail.slopes[head] : 0.f;
 
   float o[kVQ];
 #pragma unroll
@@ -411,7 +421,7 @@ maps_prefill_kernel(const MapsPrefillArgs<T> a) {
         float v = 0.f;
         if (j < k_end && !dead_key(j, pos0, a.mask)) {
           const size_t page = bt[j / a.page_size];
-          v = to_float(a.vcache[((page * a.kv_heads + kvh) * a.page_size + j % a.page_size) * kDV + d]);
+          v = to_float(a.vcache[((page * a.kv_heads + kvh) * a.page_size + j % a.page_size) * kVS + d]);
         }
         Vs[key * kDV + d] = v;
       }
@@ -431,6 +441,7 @@ maps_prefill_kernel(const MapsPrefillArgs<T> a) {
         const bool ok = (r < rows) && key_visible(kp, my_pos, a.mask);
         float v = s[i];
         if (a.softcap > 0.f) v = a.softcap * tanhf(v * inv_cap);
+        v -= slope * static_cast<float>(my_pos - kp);
         s[i] = ok ? v : -INFINITY;
         tmax = fmaxf(tmax, s[i]);
       }
@@ -502,7 +513,7 @@ maps_prefill_kernel(const MapsPrefillArgs<T> a) {
 // into the same float32 accumulator), which keeps 16 bits of mantissa.  Both maps run in turn over the
 // visible tiles; the first map's result waits in shared memory; combination, unit norm and the bfloat16
 // store are the epilogue.
-#if (RL_QK_DIM % 16 == 0) && (RL_V_DIM % 16 == 0)
+#if (RL_QK_DIM % 16 == 0) && (RL_V_DIM % 16 == 0) && (RL_V_STRIDE % 8 == 0)
 #define RL_MAPS_HAVE_MMA 1
 constexpr int kTQ = 64, kTK = 64;
 constexpr int kLDK = kD + 8, kLDV = kDV + 8;      // shared-memory row lengths in elements
@@ -555,6 +566,7 @@ maps_prefill_mma_kernel(const MapsPrefillArgs<bf16> a) {
   const int p0 = pos0 + r0, p1 = pos0 + r1;
   const bool ok0 = r0 < rows, ok1 = r1 < rows;
   const float inv_cap = a.softcap > 0.f ? 1.f / a.softcap : 0.f;
+  const float slope = a.tail.slopes != nullptr ? a.tail.slopes[head] : 0.f;
   const int ps_shift = __ffs(a.page_size) - 1, ps_mask = a.page_size - 1;      // (pages hold a power of two of tokens)
 
   float o[kDV / 8][4];
@@ -603,7 +615,7 @@ maps_prefill_mma_kernel(const MapsPrefillArgs<bf16> a) {
         bf16* d = Vd + key * kLDV + c * 8;
         if (j < k_end && !dead_key(j, pos0, a.mask)) {
           const size_t page = bt[j >> ps_shift];
-          cp_async16(d, a.vcache + ((page * a.kv_heads + kvh) * a.page_size + (j & ps_mask)) * kDV + c * 8);
+          cp_async16(d, a.vcache + ((page * a.kv_heads + kvh) * a.page_size + (j & ps_mask)) * kVS + c * 8);
         } else {
           *reinterpret_cast<uint4*>(d) = make_uint4(0, 0, 0, 0);
         }
@@ -650,6 +662,7 @@ maps_prefill_mma_kernel(const MapsPrefillArgs<bf16> a) {
           const int j = k0 + nt * 8 + tig * 2 + (e & 1);
           float v = s[nt][e] * a.scale;
           if (a.softcap > 0.f) v = a.softcap * tanh_fast(v * inv_cap);
+          v -= slope * static_cast<float>(((e < 2) ? p0 : p1) - j);
           const bool vis = (e < 2) ? (ok0 && key_visible(j, p0, a.mask)) : (ok1 && key_visible(j, p1, a.mask));
           v = vis ? v : -INFINITY;
           s[nt][e] = v;
@@ -812,9 +825,10 @@ int launch_maps_decode(const void* q, int q_stride, const void* kc, const void* 
                        const int32_t* items, float* part_o, float* part_ml, int max_parts, void* out, int out_stride,
                        int nitems, int heads, int kv_heads, int page_size, int window, int keep_first, float scale,
                        float softcap, float lambda, float post_scale, float eps, int unit_norm, const float* sink,
-                       const void* gate, int gate_stride, int gate_mode, cudaStream_t stream) {
+                       const float* slopes, const void* gate, int gate_stride, int gate_mode, cudaStream_t stream) {
   MapsDecodeArgs<T> a;
   a.tail.sink = sink;
+  a.tail.slopes = slopes;
   a.tail.gate = static_cast<const T*>(gate);
   a.tail.gate_stride = gate_stride;
   a.tail.gate_mode = gate == nullptr ? 0 : gate_mode;
@@ -852,10 +866,12 @@ int launch_maps_prefill(const void* q, int q_stride, const void* kc, const void*
                         const int32_t* tile_seq, const int32_t* tile_tok, const int32_t* tile_rows,
                         const int32_t* positions, void* out, int out_stride, int tiles, int tile_rows_max, int heads,
                         int kv_heads, int page_size, int window, int keep_first, float scale, float softcap,
-                        float lambda, float post_scale, float eps, int unit_norm, const float* sink, const void* gate,
-                        int gate_stride, int gate_mode, int impl, cudaStream_t stream) {
+                        float lambda, float post_scale, float eps, int unit_norm, const float* sink,
+                        const float* slopes, const void* gate, int gate_stride, int gate_mode, int impl,
+                        cudaStream_t stream) {
   MapsPrefillArgs<T> a;
   a.tail.sink = sink;
+  a.tail.slopes = slopes;
   a.tail.gate = static_cast<const T*>(gate);
   a.tail.gate_stride = gate_stride;
   a.tail.gate_mode = gate == nullptr ? 0 : gate_mode;
@@ -923,32 +939,33 @@ int rl_maps_decode(int dtype, const void* q, int q_stride, const void* kc, const
                    int max_blocks, const int32_t* items, float* part_o, float* part_ml, int max_parts, void* out,
                    int out_stride, int nitems, int heads, int kv_heads, int page_size, int window, int keep_first,
                    float scale, float softcap, float lambda, float post_scale, float eps, int unit_norm,
-                   const float* sink, const void* gate, int gate_stride, int gate_mode, cudaStream_t stream) {
+                   const float* sink, const float* slopes, const void* gate, int gate_stride, int gate_mode,
+                   cudaStream_t stream) {
   if (nitems <= 0 || max_parts <= 0) return 0;
   if (dtype == 0)
     return launch_maps_decode<float>(q, q_stride, kc, vc, bt, max_blocks, items, part_o, part_ml, max_parts, out,
                                      out_stride, nitems, heads, kv_heads, page_size, window, keep_first, scale, softcap,
-                                     lambda, post_scale, eps, unit_norm, sink, gate, gate_stride, gate_mode, stream);
+                                     lambda, post_scale, eps, unit_norm, sink, slopes, gate, gate_stride, gate_mode, stream);
   return launch_maps_decode<bf16>(q, q_stride, kc, vc, bt, max_blocks, items, part_o, part_ml, max_parts, out,
                                   out_stride, nitems, heads, kv_heads, page_size, window, keep_first, scale, softcap,
-                                  lambda, post_scale, eps, unit_norm, sink, gate, gate_stride, gate_mode, stream);
+                                  lambda, post_scale, eps, unit_norm, sink, slopes, gate, gate_stride, gate_mode, stream);
 }
 
 int rl_maps_prefill(int dtype, const void* q, int q_stride, const void* kc, const void* vc, const int32_t* bt,
                     int max_blocks, const int32_t* tile_seq, const int32_t* tile_tok, const int32_t* tile_rows,
                     const int32_t* positions, void* out, int out_stride, int tiles, int tile_rows_max, int heads,
                     int kv_heads, int page_size, int window, int keep_first, float scale, float softcap, float lambda,
-                    float post_scale, float eps, int unit_norm, const float* sink, const void* gate, int gate_stride,
-                    int gate_mode, int impl, cudaStream_t stream) {
+                    float post_scale, float eps, int unit_norm, const float* sink, const float* slopes, const void* gate,
+                    int gate_stride, int gate_mode, int impl, cudaStream_t stream) {
   if (tiles <= 0) return 0;
   if (dtype == 0)
     return launch_maps_prefill<float>(q, q_stride, kc, vc, bt, max_blocks, tile_seq, tile_tok, tile_rows, positions,
                                       out, out_stride, tiles, tile_rows_max, heads, kv_heads, page_size, window,
-                                      keep_first, scale, softcap, lambda, post_scale, eps, unit_norm, sink, gate, gate_stride,
+                                      keep_first, scale, softcap, lambda, post_scale, eps, unit_norm, sink, slopes, gate, gate_stride,
                                       gate_mode, impl, stream);
   return launch_maps_prefill<bf16>(q, q_stride, kc, vc, bt, max_blocks, tile_seq, tile_tok, tile_rows, positions,
                                    out, out_stride, tiles, tile_rows_max, heads, kv_heads, page_size, window,
-                                   keep_first, scale, softcap, lambda, post_scale, eps, unit_norm, sink, gate, gate_stride,
+                                   keep_first, scale, softcap, lambda, post_scale, eps, unit_norm, sink, slopes, gate, gate_stride,
                                       gate_mode, impl, stream);
 }
 

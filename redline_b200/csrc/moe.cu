@@ -4,7 +4,11 @@
 //   router:   z = W_r x (float32 sums; in this kernel, or handed in as float32 logits), score = sigmoid(z) (or softmax over the experts); experts lie in
 //             `groups` equal groups of neighbours; a group's score is the sum of its `group_top` best
 //             scores; only experts of the best `keep` groups can be chosen; the `top` best of those are
-//             the token's experts, weighted by their scores (optionally divided by their sum)
+//             the token's experts, weighted by their scores (optionally divided by their sum);
+//             a choice bias per expert may be added to the scores for the choice alone (the weights are the
+//             scores without it); the weights may be multiplied by a constant
+//   identity: router outputs beyond the experts that have matrices stand for the input itself: their pairs
+//             get no tiles, and the combine kernel takes the token's input row in place of a product
 //   pairs:    pair p = token * top + k; `order` lists the pairs expert by expert, `tile_expert` /
 //             `tile_begin` / `tile_rows` cut every expert's pairs into tiles of up to 64 rows
 //   products: up:   act[p, :]  = f(W_up[e]   x[token(p), :])      f = activation
@@ -54,7 +58,8 @@ __device__ __forceinline__ ArgMax warp_argmax(ArgMax a) {
 template <typename TA, typename TW>
 __global__ void moe_route_kernel(const TA* __restrict__ x, int ld, const TW* __restrict__ router, int tokens,
                                  int width, int experts, int groups, int keep, int group_top, int top, int softmax,
-                                 int renorm, const float* __restrict__ bias, int32_t* __restrict__ choice,
+                                 int renorm, const float* __restrict__ bias, const float* __restrict__ choice_bias,
+                                 float weight_scale, float renorm_floor, int32_t* __restrict__ choice,
                                  float* __restrict__ weight) {
   pdl_launch();
   pdl_wait();
@@ -96,7 +101,7 @@ __global__ void moe_route_kernel(const TA* __restrict__ x, int ld, const TW* __r
     for (int e = lane; e < experts; e += 32) score[e] = 1.f / (1.f + expf(-score[e]));
   }
   __syncwarp();
-  for (int e = lane; e < experts; e += 32) work[e] = score[e];
+  for (int e = lane; e < experts; e += 32) work[e] = score[e] + (choice_bias != nullptr ? choice_bias[e] : 0.f);
   __syncwarp();
   const int per = experts / groups;
   if (groups > 1 && keep < groups) {
@@ -166,8 +171,12 @@ __global__ void moe_route_kernel(const TA* __restrict__ x, int ld, const TW* __r
     if (found) total += score[a.i];
     __syncwarp();
   }
-  if (renorm && lane == 0) {
-    for (int k = 0; k < top; ++k) weight[static_cast<size_t>(t) * top + k] /= total;
+  if (lane == 0 && (renorm || weight_scale != 1.f)) {
+    for (int k = 0; k < top; ++k) {
+      float wk = weight[static_cast<size_t>(t) * top + k];
+      if (renorm) wk /= total + renorm_floor;
+      weight[static_cast<size_t>(t) * top + k] = wk * weight_scale;
+    }
   }
 }
 
@@ -175,7 +184,7 @@ __global__ void moe_route_kernel(const TA* __restrict__ x, int ld, const TW* __r
 // One CTA.  counts -> offsets -> order; then the tiles.  meta: [0] number of tiles.
 constexpr int kTileRows = 64;
 
-__global__ void moe_group_kernel(const int32_t* __restrict__ choice, int pairs, int experts,
+__global__ void moe_group_kernel(const int32_t* __restrict__ choice, int pairs, int experts, int tiled,
                                  int32_t* __restrict__ order, int32_t* __restrict__ tile_expert,
                                  int32_t* __restrict__ tile_begin, int32_t* __restrict__ tile_rows,
                                  int32_t* __restrict__ meta) {
@@ -191,7 +200,7 @@ __global__ void moe_group_kernel(const int32_t* __restrict__ choice, int pairs, 
     int at = 0, tiles = 0;
     for (int e = 0; e < experts; ++e) {
       off[e] = at;
-      for (int r = 0; r < cnt[e]; r += kTileRows) {
+      for (int r = 0; r < cnt[e] && e < tiled; r += kTileRows) {      // (experts from `tiled` on have no matrices)
         tile_expert[tiles] = e;
         tile_begin[tiles] = at + r;
         tile_rows[tiles] = min(kTileRows, cnt[e] - r);
@@ -483,14 +492,20 @@ moe_gemv_kernel(const T* __restrict__ src, int ld_src, int src_div, const T* __r
 // out[t, c] = sum_k weight[t, k] * y[t * top + k, c] (+ shared[t, c])
 template <typename TA>
 __global__ void moe_combine_kernel(const TA* __restrict__ y, const float* __restrict__ weight,
-                                   const TA* __restrict__ shared, TA* __restrict__ out, int width, int top) {
+                                   const TA* __restrict__ shared, TA* __restrict__ out, int width, int top,
+                                   const int32_t* __restrict__ choice, int real_experts, const TA* __restrict__ x,
+                                   int ld_x) {
   pdl_launch();
   pdl_wait();
   const int t = blockIdx.y;
   for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < width; c += gridDim.x * blockDim.x) {
     float s = 0.f;
-    for (int k = 0; k < top; ++k)
-      s = fmaf(weight[static_cast<size_t>(t) * top + k], to_float(y[(static_cast<size_t>(t) * top + k) * width + c]), s);
+    for (int k = 0; k < top; ++k) {
+      const size_t pair = static_cast<size_t>(t) * top + k;
+      // (an identity expert's pair has no product: its term is the token's input row)
+      const bool same = choice != nullptr && choice[pair] >= real_experts;
+      s = fmaf(weight[pair], same ? to_float(x[static_cast<size_t>(t) * ld_x + c]) : to_float(y[pair * width + c]), s);
+    }
     if (shared != nullptr) s += to_float(shared[static_cast<size_t>(t) * width + c]);
     out[static_cast<size_t>(t) * width + c] = from_float<TA>(s);
   }
@@ -506,7 +521,8 @@ int rl_moe_tile_rows() { return kTileRows; }
 
 int rl_moe_route(const void* x, int act_dtype, int ld, const void* router, int w_dtype, int tokens, int width,
                  int experts, int groups, int keep, int group_top, int top, int softmax, int renorm, const float* bias,
-                 int32_t* choice, float* weight, cudaStream_t stream) {
+                 const float* choice_bias, float weight_scale, float renorm_floor, int32_t* choice, float* weight,
+                 cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const int warps = 4;
   const size_t smem = static_cast<size_t>(warps) * (2 * experts + 2 * groups) * sizeof(float);
@@ -514,7 +530,7 @@ int rl_moe_route(const void* x, int act_dtype, int ld, const void* router, int w
 #define RL_CASE(TA, TW)                                                                                            \
   launch_kernel(moe_route_kernel<TA, TW>, grid, block, smem, stream, static_cast<const TA*>(x), ld,                \
                 static_cast<const TW*>(router), tokens, width, experts, groups, keep, group_top, top, softmax,     \
-                renorm, bias, choice, weight)
+                renorm, bias, choice_bias, weight_scale, renorm_floor, choice, weight)
   if (act_dtype == 0) RL_CASE(float, float);
   else if (w_dtype == 0) RL_CASE(bf16, float);
   else RL_CASE(bf16, bf16);
@@ -522,11 +538,11 @@ int rl_moe_route(const void* x, int act_dtype, int ld, const void* router, int w
   RL_LAUNCH_END();
 }
 
-int rl_moe_group(const int32_t* choice, int pairs, int experts, int32_t* order, int32_t* tile_expert,
+int rl_moe_group(const int32_t* choice, int pairs, int experts, int tiled, int32_t* order, int32_t* tile_expert,
                  int32_t* tile_begin, int32_t* tile_rows, int32_t* meta, cudaStream_t stream) {
   if (pairs <= 0) return 0;
   launch_kernel(moe_group_kernel, dim3(1), dim3(256), (2 * experts + 1) * sizeof(int32_t), stream, choice, pairs,
-                experts, order, tile_expert, tile_begin, tile_rows, meta);
+                experts, tiled, order, tile_expert, tile_begin, tile_rows, meta);
   RL_LAUNCH_END();
 }
 
@@ -569,15 +585,18 @@ int rl_moe_gemm(int act_dtype, const void* src, int ld_src, int src_div, const v
 }
 
 int rl_moe_combine(int act_dtype, const void* y, const float* weight, const void* shared, void* out, int tokens,
-                   int width, int top, cudaStream_t stream) {
+                   int width, int top, const int32_t* choice, int real_experts, const void* x, int ld_x,
+                   cudaStream_t stream) {
   if (tokens <= 0) return 0;
   dim3 grid(min((width + 255) / 256, 32), tokens);
   if (act_dtype == 0)
     launch_kernel(moe_combine_kernel<float>, grid, dim3(256), 0, stream, static_cast<const float*>(y), weight,
-                  static_cast<const float*>(shared), static_cast<float*>(out), width, top);
+                  static_cast<const float*>(shared), static_cast<float*>(out), width, top, choice, real_experts,
+                  static_cast<const float*>(x), ld_x);
   else
     launch_kernel(moe_combine_kernel<bf16>, grid, dim3(256), 0, stream, static_cast<const bf16*>(y), weight,
-                  static_cast<const bf16*>(shared), static_cast<bf16*>(out), width, top);
+                  static_cast<const bf16*>(shared), static_cast<bf16*>(out), width, top, choice, real_experts,
+                  static_cast<const bf16*>(x), ld_x);
   RL_LAUNCH_END();
 }
 

@@ -15,6 +15,7 @@ from ..cache.manager import GroupInfo
 from ..parts import base as parts_base
 from ..parts.base import Block, Runtime, build_part, lookup, op_mark
 from ..parts.spec import CacheSpec, ModelSpec, StateSpec, TensorSpec
+from ..ops import kernels
 from ..weights import loader
 from ..weights.safetensors_io import CheckpointReader
 
@@ -167,8 +168,23 @@ class DecoderModel:
         op_mark(ctx, "embed", nbytes=T * self.spec.hidden_size * (4.0 + (2 if rt.dtype == torch.bfloat16 else 4)))
         pending = None
         order = self.spec.order
+        embedded = None
+        if any(call.add_embedding for call in order):
+            # the embedding output once more, for the calls that add it to the stream again
+            embedded = ws.get("embedded", (rt.max_tokens, self.spec.hidden_size), torch.float32)[:T]
+            self.embedding.forward(ctx, embedded)
+            op_mark(ctx, "embed", nbytes=T * self.spec.hidden_size * (4.0 + (2 if rt.dtype == torch.bfloat16 else 4)))
         ctx.block_hand = ctx.block_normed = None
         for i, call in enumerate(order):
+            if call.add_embedding:
+                # residual += what the block before left to add, and the embedding output; nothing of the
+                # block before reaches across (its handed-over norm was of the stream without the addend)
+                if pending is not None:
+                    kernels.add_residual(residual, pending)
+                    pending = None
+                kernels.add_residual(residual, embedded)
+                op_mark(ctx, "add_embedding", nbytes=T * self.spec.hidden_size * 12.0)
+                ctx.block_hand = ctx.block_normed = None
             # (the block after this one may take over its first norm from this block's last kernel)
             ctx.block_next = self.blocks[order[i + 1].layer] if i + 1 < len(order) else None
             ctx.block_next_norm = ctx.block_next.first_norm() if ctx.block_next is not None else None

@@ -1,3 +1,3 @@
 """Built-in architectures; importing this package registers them."""
 
-from . import kapitar, llama, pufevik, vizotar  # noqa: F401
+from . import kapitar, llama, pufevik, venezen, vizotar  # noqa: F401

@@ -718,12 +718,19 @@ def head_prep(x: torch.Tensor, positions: torch.Tensor, tokens: int, q_col: int,
 
 # ------------------------------------ attention with score maps, a capped score and kept first tokens
 
-def _maps(dim: int, vdim: int, maps: int) -> ctypes.CDLL:
+def _maps(dim: int, vdim: int, maps: int, v_stride: int = 0) -> ctypes.CDLL:
+    """``v_stride``: the length of a row of the value cache when it is longer than a value (a mixer whose
+    values are the leading entries of its keys hands the key cache in as the value cache); 0: ``vdim``."""
     if not (1 <= dim <= 256 and 1 <= vdim <= 256 and maps in (1, 2)):
         raise KernelError(f"attention_maps takes key and value sizes up to 256 and one or two maps; "
                           f"got {dim}, {vdim}, {maps}")
-    return _lib(f"attention_maps_d{dim}_v{vdim}_m{maps}", "attention_maps.cu",
-                {"RL_QK_DIM": dim, "RL_V_DIM": vdim, "RL_MAPS": maps})
+    if v_stride in (0, vdim):
+        return _lib(f"attention_maps_d{dim}_v{vdim}_m{maps}", "attention_maps.cu",
+                    {"RL_QK_DIM": dim, "RL_V_DIM": vdim, "RL_MAPS": maps})
+    if v_stride < vdim:
+        raise KernelError(f"attention_maps: a value row of {v_stride} entries cannot hold a value of {vdim}")
+    return _lib(f"attention_maps_d{dim}_v{vdim}_m{maps}_s{v_stride}", "attention_maps.cu",
+                {"RL_QK_DIM": dim, "RL_V_DIM": vdim, "RL_MAPS": maps, "RL_V_STRIDE": v_stride})
 
 
 def maps_attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcache: torch.Tensor,
@@ -732,19 +739,21 @@ def maps_attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcach
                      maps: int, page_size: int, window: int, keep_first: int, scale: float, softcap: float,
                      lam: float, post_scale: float, eps: float, unit_norm: bool,
                      sink: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None,
-                     gate_mode: int = 0) -> None:
+                     gate_mode: int = 0, slopes: Optional[torch.Tensor] = None, v_stride: int = 0) -> None:
     """One query token per item (``items`` as for ``attn_decode``) over the paged cache, ``maps`` score maps
     per head over shared values (csrc/attention_maps.cu): q rows (head, map) of ``dim``, key cache
     [pages, kv_heads * maps, page, dim], value cache [pages, kv_heads, page, vdim], out heads of ``vdim``.
     ``sink`` (float32 [heads], one map only) joins every head's softmax denominator; ``gate`` (a row-strided
     view of q's type) multiplies the output by its sigmoid, per head (``gate_mode`` 1, [tokens, heads]) or
-    per entry (2, [tokens, heads * vdim]); ``post_scale`` multiplies the output too."""
-    _need_cuda(q, kcache, vcache, out, sink, gate)
-    _check_tail(maps, heads, vdim, q, sink, gate, gate_mode)
-    f = _fn(_maps(dim, vdim, maps), "rl_maps_decode",
+    per entry (2, [tokens, heads * vdim]); ``post_scale`` multiplies the output too.  ``slopes`` (float32
+    [heads]): slope_h times the distance between query and key is taken off every score of head h.
+    ``v_stride``: see ``_maps``."""
+    _need_cuda(q, kcache, vcache, out, sink, gate, slopes)
+    _check_tail(maps, heads, vdim, q, sink, gate, gate_mode, slopes)
+    f = _fn(_maps(dim, vdim, maps, v_stride), "rl_maps_decode",
             [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p,
              c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float, c_float, c_int,
-             c_void_p, c_void_p, c_int, c_int, c_void_p])
+             c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p])
     need = nitems * heads * maps * max_parts
     if part_o.numel() < need * vdim or part_ml.numel() < need * 2:
         raise KernelError("maps_attn_decode: partition workspace too small")
@@ -753,12 +762,14 @@ def maps_attn_decode(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcach
     _check(f(_code(q.dtype), _ptr(q), q_stride, _ptr(kcache), _ptr(vcache), _ptr(block_table), block_table.shape[1],
              _ptr(items), _ptr(part_o), _ptr(part_ml), max_parts, _ptr(out), out.stride(0), nitems, heads, kv_heads,
              page_size, window, keep_first, float(scale), float(softcap), float(lam), float(post_scale), float(eps),
-             1 if unit_norm else 0, _ptr(sink), _ptr(gate), gate.stride(0) if gate is not None else 0,
+             1 if unit_norm else 0, _ptr(sink), _ptr(slopes), _ptr(gate), gate.stride(0) if gate is not None else 0,
              gate_mode if gate is not None else 0, _stream()), "maps_attn_decode", 2)
 
 
 def _check_tail(maps: int, heads: int, vdim: int, q: torch.Tensor, sink: Optional[torch.Tensor],
-                gate: Optional[torch.Tensor], gate_mode: int) -> None:
+                gate: Optional[torch.Tensor], gate_mode: int, slopes: Optional[torch.Tensor] = None) -> None:
+    if slopes is not None and (slopes.dtype != torch.float32 or slopes.numel() != heads or not slopes.is_contiguous()):
+        raise KernelError("attention_maps: the distance slopes are float32 [heads]")
     if sink is not None and (maps != 1 or sink.dtype != torch.float32 or sink.numel() != heads
                              or not sink.is_contiguous()):
         raise KernelError("attention_maps: a sink is float32 [heads] and goes with one score map")
@@ -773,22 +784,74 @@ def maps_attn_prefill(q: torch.Tensor, q_stride: int, kcache: torch.Tensor, vcac
                       tile_rows_max: int, heads: int, kv_heads: int, dim: int, vdim: int, maps: int, page_size: int,
                       window: int, keep_first: int, scale: float, softcap: float, lam: float, post_scale: float,
                       eps: float, unit_norm: bool, sink: Optional[torch.Tensor] = None,
-                      gate: Optional[torch.Tensor] = None, gate_mode: int = 0, impl: int = 0) -> None:
+                      gate: Optional[torch.Tensor] = None, gate_mode: int = 0, impl: int = 0,
+                      slopes: Optional[torch.Tensor] = None, v_stride: int = 0) -> None:
     """Tiles of up to ``tile_rows_max`` consecutive query tokens of one sequence; otherwise as
     ``maps_attn_decode``.  impl 0: the best kernel that applies (bfloat16 with sizes that are multiples of
     16: mma.sync tensor cores; else CUDA cores); 1: CUDA cores; 2: the tensor-core kernel or an error."""
-    _need_cuda(q, kcache, vcache, out, sink, gate)
-    _check_tail(maps, heads, vdim, q, sink, gate, gate_mode)
-    f = _fn(_maps(dim, vdim, maps), "rl_maps_prefill",
+    _need_cuda(q, kcache, vcache, out, sink, gate, slopes)
+    _check_tail(maps, heads, vdim, q, sink, gate, gate_mode, slopes)
+    f = _fn(_maps(dim, vdim, maps, v_stride), "rl_maps_prefill",
             [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
              c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_float, c_float,
-             c_float, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
+             c_float, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
     _check(f(_code(q.dtype), _ptr(q), q_stride, _ptr(kcache), _ptr(vcache), _ptr(block_table), block_table.shape[1],
              _ptr(tile_seq), _ptr(tile_tok), _ptr(tile_rows), _ptr(positions), _ptr(out), out.stride(0), tiles,
              tile_rows_max, heads, kv_heads, page_size, window, keep_first, float(scale), float(softcap), float(lam),
-             float(post_scale), float(eps), 1 if unit_norm else 0, _ptr(sink), _ptr(gate),
+             float(post_scale), float(eps), 1 if unit_norm else 0, _ptr(sink), _ptr(slopes), _ptr(gate),
              gate.stride(0) if gate is not None else 0, gate_mode if gate is not None else 0, impl, _stream()),
            "maps_attn_prefill")
+
+
+# ------------------------------------------------------- attention over a cached latent
+
+def _latent() -> ctypes.CDLL:
+    return _lib("latent", "latent.cu")
+
+
+def latent_prep(proj: torch.Tensor, positions: torch.Tensor, tokens: int, heads: int, dn: int, dr: int, rank: int,
+                rot_dims: int, norm_w: torch.Tensor, eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                qa: torch.Tensor, slots: Optional[torch.Tensor], cache: torch.Tensor, page_size: int,
+                status: torch.Tensor) -> None:
+    """Rows of ``proj``: per head a query [dn unrotated | dr rotated], then [latent of ``rank`` | key part of dr].
+    The latent is RMS-normed (float32, weight ``norm_w``); the key part and every head's rotated query part turn
+    by the token's position (the first ``rot_dims`` rotated entries, entry i with i + rot_dims/2; cos / sin
+    float32 [positions, rot_dims/2]); [latent | key part] goes into ``cache`` [pages, 1, page, rank + dr] at the
+    token's slot (negative: not written), the rotated query parts into columns [rank, rank + dr) of every
+    head of ``qa`` [tokens, heads * (rank + dr)] (csrc/latent.cu)."""
+    _need_cuda(proj, positions, norm_w, cos, sin, qa, slots, cache)
+    if proj.dtype != qa.dtype or proj.dtype != cache.dtype or proj.stride(1) != 1 or qa.stride(1) != 1 \
+            or not cache.is_contiguous() or norm_w.numel() != rank:
+        raise KernelError("latent_prep: projection, query rows and cache have one type and contiguous rows")
+    if dr > 0 and (cos is None or sin is None or cos.dtype != torch.float32 or cos.shape[1] * 2 != rot_dims
+                   or rot_dims > dr or not cos.is_contiguous() or not sin.is_contiguous()):
+        raise KernelError("latent_prep: cos / sin are float32 [positions, rot_dims / 2], rot_dims at most dr")
+    if proj.shape[1] < heads * (dn + dr) + rank + dr or qa.shape[1] < heads * (rank + dr):
+        raise KernelError("latent_prep: rows too short for the heads and the latent")
+    f = _fn(_latent(), "rl_latent_prep",
+            [c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float,
+             c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_void_p, c_void_p])
+    _check(f(_code(proj.dtype), _code(norm_w.dtype), _ptr(proj), proj.stride(0), _ptr(positions), tokens, heads, dn, dr,
+             rank, rot_dims if dr > 0 else 0, _ptr(norm_w), float(eps), _ptr(cos), _ptr(sin),
+             cos.shape[0] if cos is not None else 0, _ptr(qa), qa.stride(0), _ptr(slots), _ptr(cache), page_size,
+             cache.shape[0] * page_size, _ptr(status), _stream()), "latent_prep")
+
+
+def head_linear(x: torch.Tensor, x_col: int, x_head: int, w: torch.Tensor, y: torch.Tensor, y_col: int, y_head: int,
+                tokens: Optional[int] = None, impl: int = 0) -> None:
+    """y[t, y_col + h * y_head + j] = sum_k w[h, j, k] * x[t, x_col + h * x_head + k] for every head h:
+    w [heads, n, k]; float32 sums in ascending k.  impl 1: CUDA cores also where the tensor cores apply."""
+    _need_cuda(x, w, y)
+    heads, n, k = w.shape
+    if x.dtype != y.dtype or x.stride(1) != 1 or y.stride(1) != 1 or not w.is_contiguous() \
+            or (x.dtype == torch.float32 and w.dtype != torch.float32):
+        raise KernelError("head_linear: x and y have one type and contiguous rows; w contiguous [heads, n, k]")
+    if x_col + (heads - 1) * x_head + k > x.shape[1] or y_col + (heads - 1) * y_head + n > y.shape[1]:
+        raise KernelError("head_linear: the heads do not fit the rows")
+    f = _fn(_latent(), "rl_head_linear", [c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int,
+                                          c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p])
+    _check(f(_code(x.dtype), _code(w.dtype), _ptr(x), x.stride(0), x_col, x_head, _ptr(w), heads, n, k, _ptr(y),
+             y.stride(0), y_col, y_head, tokens if tokens is not None else x.shape[0], impl, _stream()), "head_linear")
 
 
 # ------------------------------------------------------- linear attention with a decaying state
@@ -1071,13 +1134,18 @@ def moe_max_tiles(pairs: int, experts: int) -> int:
 
 def moe_route(x: torch.Tensor, router: Optional[torch.Tensor], choice: torch.Tensor, weight: torch.Tensor, tokens: int,
               groups: int, keep: int, group_top: int, top: int, softmax: bool = False, renorm: bool = False,
-              bias: Optional[torch.Tensor] = None) -> None:
+              bias: Optional[torch.Tensor] = None, choice_bias: Optional[torch.Tensor] = None,
+              weight_scale: float = 1.0, renorm_floor: float = 0.0) -> None:
     """Per token: scores of the experts (float32 sums; sigmoid, or softmax), the best ``keep`` of ``groups``
     groups of neighbouring experts by the sum of their ``group_top`` best scores, the ``top`` best experts
     of those into choice [tokens, top] int32 with their scores in weight [tokens, top] float32.  With
     ``router`` None, ``x`` holds the logits themselves, float32 [tokens, experts].  ``bias`` (float32
-    [experts]) is added to the logits before they are scored."""
-    _need_cuda(x, router, choice, weight, bias)
+    [experts]) is added to the logits before they are scored.  ``choice_bias`` (float32 [experts]) is added to
+    the scores for the choice only: the weights are the scores without it.  With ``renorm`` the chosen scores
+    are divided by their sum + ``renorm_floor``; every weight is multiplied by ``weight_scale``."""
+    _need_cuda(x, router, choice, weight, bias, choice_bias)
+    if choice_bias is not None and (choice_bias.dtype != torch.float32 or not choice_bias.is_contiguous()):
+        raise KernelError("moe_route: the choice bias is contiguous float32 [experts]")
     if bias is not None and (bias.dtype != torch.float32 or not bias.is_contiguous() or bias.numel() != x.shape[1] and router is None):
         raise KernelError("moe_route: the bias is contiguous float32 [experts]")
     if router is None:
@@ -1089,22 +1157,28 @@ def moe_route(x: torch.Tensor, router: Optional[torch.Tensor], choice: torch.Ten
     if experts % max(groups, 1) != 0 or choice.dtype != torch.int32 or weight.dtype != torch.float32 \
             or x.stride(1) != 1 or (router is not None and not router.is_contiguous()):
         raise KernelError("moe_route: experts must divide into the groups; choice int32, weight float32")
+    if choice_bias is not None and choice_bias.numel() != experts:
+        raise KernelError("moe_route: one choice bias per expert")
     f = _fn(_moe(), "rl_moe_route", [c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                                      c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p])
+                                      c_int, c_int, c_int, c_void_p, c_void_p, c_float, c_float, c_void_p, c_void_p,
+                                      c_void_p])
     _check(f(_ptr(x), _code(x.dtype), x.stride(0), _ptr(router), _code(router.dtype) if router is not None else 0,
              tokens, width, experts,
-             max(groups, 1), keep, group_top, top, 1 if softmax else 0, 1 if renorm else 0, _ptr(bias), _ptr(choice),
-             _ptr(weight), _stream()), "moe_route")
+             max(groups, 1), keep, group_top, top, 1 if softmax else 0, 1 if renorm else 0, _ptr(bias),
+             _ptr(choice_bias), float(weight_scale), float(renorm_floor), _ptr(choice), _ptr(weight), _stream()),
+           "moe_route")
 
 
 def moe_group(choice: torch.Tensor, pairs: int, experts: int, order: torch.Tensor, tile_expert: torch.Tensor,
-              tile_begin: torch.Tensor, tile_rows: torch.Tensor, meta: torch.Tensor) -> None:
+              tile_begin: torch.Tensor, tile_rows: torch.Tensor, meta: torch.Tensor, tiled: Optional[int] = None) -> None:
     """Lists the (token, slot) pairs expert by expert (``order``) and cuts every expert's list into tiles of
-    up to 64 pairs (``tile_*``, their number in meta[0]); all int32, the tile lists ``moe_max_tiles`` long."""
+    up to 64 pairs (``tile_*``, their number in meta[0]); all int32, the tile lists ``moe_max_tiles`` long.
+    ``tiled``: only the first so many experts get tiles (the others have no matrices: identity experts)."""
     _need_cuda(choice, order, tile_expert, tile_begin, tile_rows, meta)
-    f = _fn(_moe(), "rl_moe_group", [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p])
-    _check(f(_ptr(choice), pairs, experts, _ptr(order), _ptr(tile_expert), _ptr(tile_begin), _ptr(tile_rows),
-             _ptr(meta), _stream()), "moe_group")
+    f = _fn(_moe(), "rl_moe_group", [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                      c_void_p])
+    _check(f(_ptr(choice), pairs, experts, experts if tiled is None else tiled, _ptr(order), _ptr(tile_expert),
+             _ptr(tile_begin), _ptr(tile_rows), _ptr(meta), _stream()), "moe_group")
 
 
 def moe_gemm(src: torch.Tensor, src_div: int, w: torch.Tensor, dst: torch.Tensor, order: torch.Tensor,
@@ -1128,14 +1202,20 @@ def moe_gemm(src: torch.Tensor, src_div: int, w: torch.Tensor, dst: torch.Tensor
 
 
 def moe_combine(y: torch.Tensor, weight: torch.Tensor, shared: Optional[torch.Tensor], out: torch.Tensor,
-                tokens: int, top: int) -> None:
-    """out[t] = sum_k weight[t, k] * y[t * top + k] (+ shared[t]), k in order; y, shared and out contiguous."""
-    _need_cuda(y, weight, out)
+                tokens: int, top: int, choice: Optional[torch.Tensor] = None, real_experts: int = 0,
+                x: Optional[torch.Tensor] = None) -> None:
+    """out[t] = sum_k weight[t, k] * y[t * top + k] (+ shared[t]), k in order; y, shared and out contiguous.
+    With ``choice`` and ``x`` (the experts' input [tokens, width]) a pair whose chosen index is at least
+    ``real_experts`` stands for the identity: its term is weight[t, k] * x[t]."""
+    _need_cuda(y, weight, out, choice, x)
     if not (y.is_contiguous() and out.is_contiguous() and (shared is None or shared.is_contiguous())):
         raise KernelError("moe_combine: contiguous tensors")
-    f = _fn(_moe(), "rl_moe_combine", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p])
-    _check(f(_code(out.dtype), _ptr(y), _ptr(weight), _ptr(shared), _ptr(out), tokens, out.shape[1], top, _stream()),
-           "moe_combine")
+    if (choice is None) != (x is None) or (x is not None and (x.dtype != out.dtype or x.stride(1) != 1)):
+        raise KernelError("moe_combine: identity experts need the choices and the experts' input in out's type")
+    f = _fn(_moe(), "rl_moe_combine", [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p,
+                                        c_int, c_void_p, c_int, c_void_p])
+    _check(f(_code(out.dtype), _ptr(y), _ptr(weight), _ptr(shared), _ptr(out), tokens, out.shape[1], top, _ptr(choice),
+             real_experts, _ptr(x), x.stride(0) if x is not None else 0, _stream()), "moe_combine")
 
 
 # -------------------------------------------------------------------- sampling
@@ -1184,6 +1264,7 @@ def build_all(head_dims=(64, 128), maps_dims=((64, 128, 2), (128, 128, 1)), line
         build.compile_module("sampling", "sampling.cu", verbose=verbose),
         build.compile_module("rowwise", "rowwise.cu", verbose=verbose),
         build.compile_module("moe", "moe.cu", verbose=verbose),
+        build.compile_module("latent", "latent.cu", verbose=verbose),
         build.compile_module("stream_ops", "stream_ops.cu", verbose=verbose),
         build.compile_module("host_core", "host_core.cpp", verbose=verbose),   # host-only: cache manager, batch filler
     ]

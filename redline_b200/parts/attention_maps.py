@@ -18,6 +18,10 @@ the layer that provides them, "blend" in those that use them: v <- (1 - lam) v +
 is what is cached).  ``conv_taps``: a short causal convolution over time on every channel of q, k and v
 directly behind the projection (and its biases), whose last inputs are the mixer's per-request state;
 ``out_bias``: a bias on the output projection; a ``rope_halves`` encoding pairs entry i with entry i + half.
+``values_are_keys``: there is no value projection, a key head's vector is also its value (one map, vdim = dim;
+only the keys are cached and the kernels read them twice); ``distance_slopes``: one number per head, times the
+distance between query and key, is taken off every score; ``sink_value``: a constant in place of the learned
+sink (0.0 adds a one to every denominator).
 
 The cache holds keys [kv_heads * maps, dim] and values [kv_heads, vdim] per token (a window group that
 keeps its first pages); sequences that bring one token go to the partitioned decode kernel, longer
@@ -63,6 +67,9 @@ class MapsAttentionParams:
     value_mix_key: str = "v"     # layers that share values name the same key
     conv_taps: int = 0           # > 0: a causal convolution over time on every channel of q, k and v, behind the projection
     out_bias: bool = False       # the output projection has a bias
+    values_are_keys: bool = False            # no W_v: v = k as projected; only k is cached
+    distance_slopes: Optional[tuple] = None  # per head: s_ij <- s_ij - slope_h * (i - j)
+    sink_value: Optional[float] = None       # a constant sink for every head (with ``sink`` False)
 
 
 @register("mixer", "maps_attention")
@@ -92,12 +99,20 @@ class MapsAttention(Mixer):
                 or p.value_mix not in ("none", "keep", "blend"):
             raise ValueError(f"maps_attention: head_norm '{p.head_norm}', gate '{p.gate}' or value_mix "
                              f"'{p.value_mix}' is not known")
-        if p.sink and p.maps != 1:
+        if (p.sink or p.sink_value is not None) and p.maps != 1:
             raise ValueError("a sink goes with one score map")
+        if p.sink and p.sink_value is not None:
+            raise ValueError("a sink is learned or a constant, not both")
+        if p.distance_slopes is not None and len(p.distance_slopes) != p.num_heads:
+            raise ValueError(f"{len(p.distance_slopes)} distance slopes for {p.num_heads} heads")
+        if p.values_are_keys and (p.maps != 1 or p.vdim != p.dim or p.bias or p.conv_taps > 0 or p.position is not None
+                                  or p.head_norm != "none" or p.value_mix != "none"):
+            raise ValueError("values_are_keys goes with one map, vdim = dim, and no bias, convolution, position "
+                             "encoding, head norm or value blend")
         self.scale = p.scale if p.scale is not None else 1.0 / math.sqrt(p.dim)
         self.q_size = p.num_heads * p.maps * p.dim
         self.k_size = p.num_kv_heads * p.maps * p.dim
-        self.v_size = p.num_kv_heads * p.vdim
+        self.v_size = 0 if p.values_are_keys else p.num_kv_heads * p.vdim
         self.qkv_size = self.q_size + self.k_size + self.v_size
         self.out_size = p.num_heads * p.vdim
         self.gate_size = {"none": 0, "head": p.num_heads, "entry": self.out_size}[p.gate]
@@ -120,7 +135,9 @@ class MapsAttention(Mixer):
 
     def cache_spec(self) -> CacheSpec:
         p = self.params
-        tensors = (CacheTensor("k", (p.num_kv_heads * p.maps, p.dim)), CacheTensor("v", (p.num_kv_heads, p.vdim)))
+        tensors = (CacheTensor("k", (p.num_kv_heads * p.maps, p.dim)),)
+        if not p.values_are_keys:
+            tensors += (CacheTensor("v", (p.num_kv_heads, p.vdim)),)
         if p.window > 0:
             return CacheSpec("window", tensors, p.window, p.keep_first)
         return CacheSpec("full", tensors)
@@ -139,6 +156,8 @@ class MapsAttention(Mixer):
             "k_bias": TensorSpec((self.k_size,), optional=not p.bias),
             "v_bias": TensorSpec((self.v_size,), optional=not p.bias),
         }
+        if p.values_are_keys:
+            del t["v"], t["v_bias"]
         if p.maps == 2:
             t.update({n: TensorSpec((p.dim,)) for n in ("lq1", "lk1", "lq2", "lk2")})
         if p.head_norm != "none":
@@ -159,7 +178,8 @@ class MapsAttention(Mixer):
         return t
 
     def fused(self) -> Dict[str, list]:
-        out = {"qkv": ["q", "k", "v"] + (["g"] if self.params.gate != "none" else [])}
+        out = {"qkv": ["q", "k"] + ([] if self.params.values_are_keys else ["v"])
+               + (["g"] if self.params.gate != "none" else [])}
         if self.params.conv_taps > 0:
             out["qkv_conv"] = ["q_conv", "k_conv", "v_conv"]
         return out
@@ -197,6 +217,11 @@ class MapsAttention(Mixer):
             self.lam = float(torch.exp((lq1 * lk1).sum()) - torch.exp((lq2 * lk2).sum()) + p.diff)
         self.w_qnorm, self.w_knorm = tensors.get("q_norm"), tensors.get("k_norm")
         self.sink = tensors["sink"].float().contiguous() if p.sink else None
+        if p.sink_value is not None:
+            self.sink = torch.full((p.num_heads,), float(p.sink_value), dtype=torch.float32, device=self.rt.device)
+        self.slopes = None
+        if p.distance_slopes is not None:
+            self.slopes = torch.tensor([float(x) for x in p.distance_slopes], dtype=torch.float32, device=self.rt.device)
         self.mix = float(tensors["vmix"].float()) if p.value_mix == "blend" else 0.0
         self.norm_mode = {"none": kernels.HEAD_NORM_NONE, "each": kernels.HEAD_NORM_EACH,
                           "whole": kernels.HEAD_NORM_WHOLE}[p.head_norm]
@@ -258,12 +283,14 @@ class MapsAttention(Mixer):
         else:
             stored = False
         g = ctx.groups[cache.group]
-        k_cache, v_cache = cache.tensors["k"], cache.tensors["v"]
+        k_cache = cache.tensors["k"]
+        v_cache = k_cache if p.values_are_keys else cache.tensors["v"]
         if cache.write and not stored:
             kernels.cache_store(qkv, self.q_size, p.num_kv_heads * p.maps, p.dim, g.slots, k_cache, rt.page_size,
                                 ctx.status, tokens=T)
-            kernels.cache_store(qkv, self.q_size + self.k_size, p.num_kv_heads, p.vdim, g.slots, v_cache,
-                                rt.page_size, ctx.status, tokens=T)
+            if not p.values_are_keys:
+                kernels.cache_store(qkv, self.q_size + self.k_size, p.num_kv_heads, p.vdim, g.slots, v_cache,
+                                    rt.page_size, ctx.status, tokens=T)
             op_mark(ctx, "kv_write", nbytes=2.0 * T * (self.k_size + self.v_size) * qkv.element_size())
         gate = gate_buf[:, self.qkv_size:] if self.gate_mode else None
         common = (p.num_heads, p.num_kv_heads, p.dim, p.vdim, p.maps, rt.page_size, p.window, p.keep_first,
@@ -274,12 +301,12 @@ class MapsAttention(Mixer):
             part_o = ws.get("mattn.part_o", (rows * p.vdim,), torch.float32)
             part_ml = ws.get("mattn.part_ml", (rows * 2,), torch.float32)
             kernels.maps_attn_decode(qkv, self.proj_size, k_cache, v_cache, g.block_table, ctx.decode_info, part_o,
-                                     part_ml, ctx.decode_parts, attn, ctx.num_decode, *common)
+                                     part_ml, ctx.decode_parts, attn, ctx.num_decode, *common, slopes=self.slopes)
             self._mark(ctx, "attention_decode", "decode")
         if ctx.num_tiles > 0:
             kernels.maps_attn_prefill(qkv, self.proj_size, k_cache, v_cache, g.block_table, ctx.tile_seq, ctx.tile_tok,
                                       ctx.tile_rows, ctx.positions, attn, ctx.num_tiles, kernels.PREFILL_TILE_ROWS,
-                                      *common)
+                                      *common, slopes=self.slopes)
             self._mark(ctx, "attention_prefill", "prefill")
 
     def _mark(self, ctx, op: str, which: str) -> None:

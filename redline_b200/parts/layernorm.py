@@ -35,6 +35,10 @@ class LayerNorm(Norm):
         return self.weight.numel() * self.weight.element_size()
 
     def add_norm(self, residual, delta, out, rows_idx=None, rows=None) -> None:
+        if rows_idx is not None and delta is not None:
+            # (the kernel norms gathered rows of the stream as it is: what is left to add goes in first)
+            kernels.add_residual(residual, delta)
+            delta = None
         kernels.sandwich_norm(residual, delta, None, self.weight, out, self.params.eps, self.kind, rows_idx, rows)
 
     def add_post_norm(self, residual: torch.Tensor, delta: torch.Tensor, next_norm: Optional["LayerNorm"],

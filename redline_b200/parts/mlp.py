@@ -78,10 +78,15 @@ class SwiGLUMLP(FeedForward):
                 + self.w_down.numel() * self.w_down.element_size())
 
     def forward(self, x, ctx) -> torch.Tensor:
+        return self.run(x, ctx, "ffn")
+
+    def run(self, x, ctx, name: str) -> torch.Tensor:
+        """The feed-forward with its buffers named after ``name`` (a part that runs one beside its own
+        feed-forward, a shared expert for instance, names another)."""
         p, rt = self.params, self.rt
         T = ctx.T
         ws = rt.workspace
-        act = ws.get("ffn.act", (rt.max_tokens, p.intermediate_size), rt.dtype)[:T]
+        act = ws.get(name + ".act", (rt.max_tokens, p.intermediate_size), rt.dtype)[:T]
         tc_epilogue = {"silu": kernels.EPI_SWIGLU, "gelu_tanh": kernels.EPI_GEGLU_TANH}.get(self.params.activation)
         if (tc_epilogue is not None and T >= TC_MIN_ROWS and self.b_gate_up is None
                 and kernels.gemm_tc_ok(x, self.w_gate_up)):
@@ -92,7 +97,7 @@ class SwiGLUMLP(FeedForward):
             # a few rows: the weight-streaming product with the gated activation in its epilogue
             kernels.gemm_skinny(self.w_gate_up, act, tc_epilogue, T, x=x)
         else:
-            gu = ws.get("ffn.gate_up", (rt.max_tokens, 2 * p.intermediate_size), rt.dtype)[:T]
+            gu = ws.get(name + ".gate_up", (rt.max_tokens, 2 * p.intermediate_size), rt.dtype)[:T]
             linear(x, self.w_gate_up, gu)
             if self.b_gate_up is not None:
                 kernels.add_bias(gu, self.b_gate_up)
@@ -103,7 +108,7 @@ class SwiGLUMLP(FeedForward):
             else:
                 kernels.gated_act(gu, act, kernels.ACTIVATIONS[self.params.activation])
         op_mark(ctx, "gate_up+swiglu" if self.silu else "gate_up+act", self.w_gate_up, T)
-        out = ws.get("ffn.out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
+        out = ws.get(name + ".out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
         linear(act, self.w_down, out)
         if self.b_down is not None:
             kernels.add_bias(out, self.b_down)

@@ -6,6 +6,13 @@ scores) can be chosen, the ``top`` best experts of those run for the token, weig
 (as they are, or divided by their sum), and a shared expert of the same form may run for every token.
 The experts' products are grouped matrix products over (token, expert) pairs listed expert by expert on
 the device (csrc/moe.cu); nothing of the routing is read by the host.
+
+Further options: ``identity`` router outputs behind the experts stand for the input itself (a chosen one adds
+weight * h and runs no product); ``choice_bias``: a number per router output that is added to the scores for
+the choice alone (the weights are the scores without it); ``renorm_floor`` joins the sum the chosen scores are
+divided by, ``weight_scale`` multiplies the weights; gated experts may use ``clamped_swish`` (gate and up
+clamped by ``limit``, g * sigmoid(slope * g) * (up + 1)); the shared expert of gated experts is gated too, with
+``shared_limit`` as its clamp.
 """
 
 from __future__ import annotations
@@ -77,6 +84,13 @@ class RoutedExpertsParams:
     shared_activation: Optional[str] = None
     gated: bool = False                  # experts are W_down (f(W_gate h) * (W_up h)) instead of W_down f(W_up h)
     router_bias: bool = False            # a bias on the router's logits
+    identity: int = 0                    # router outputs behind the experts that stand for the input itself
+    choice_bias: bool = False            # a number per router output added to the scores for the choice alone
+    weight_scale: float = 1.0            # factor on the chosen experts' weights
+    renorm_floor: float = 0.0            # renormalize: the chosen scores are divided by their sum + this
+    limit: float = 0.0                   # clamped_swish: the clamp of gate and up
+    slope: float = 1.0                   # clamped_swish: g * sigmoid(slope * g)
+    shared_limit: float = 0.0            # the shared expert's clamp (0: ``limit``)
 
 
 @register("ffn", "routed_experts")
@@ -84,31 +98,45 @@ class RoutedExperts(FeedForward):
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         p = self.params
-        if p.num_experts % p.groups != 0 or not 1 <= p.group_keep <= p.groups:
-            raise ValueError(f"{p.num_experts} experts do not form {p.groups} equal groups of which {p.group_keep} stay")
-        if not 1 <= p.top <= p.group_keep * (p.num_experts // p.groups):
+        self.outputs = p.num_experts + p.identity          # what the router scores
+        if p.identity < 0 or self.outputs % p.groups != 0 or not 1 <= p.group_keep <= p.groups:
+            raise ValueError(f"{self.outputs} router outputs do not form {p.groups} equal groups of which {p.group_keep} stay")
+        if not 1 <= p.top <= p.group_keep * (self.outputs // p.groups):
             raise ValueError(f"top {p.top} experts cannot be chosen among {p.group_keep} groups of "
-                             f"{p.num_experts // p.groups}")
+                             f"{self.outputs // p.groups}")
         if p.score not in ("sigmoid", "softmax"):
             raise ValueError(f"router score '{p.score}' is not supported (sigmoid, softmax)")
-        self.act = kernels.ACTIVATIONS[p.activation]
+        self.clamped = p.activation == "clamped_swish"
+        if self.clamped and not (p.gated and p.limit > 0):
+            raise ValueError("routed_experts: clamped_swish goes with gated experts and a positive limit")
+        self.act = kernels.ACT_CLAMPED_SWISH if self.clamped else kernels.ACTIVATIONS[p.activation]
         self.shared = None
-        if p.shared_intermediate_size > 0:
+        if p.shared_intermediate_size > 0 and p.gated:
+            from .mlp import GatedMLPParams, SwiGLUMLP
+            from .spec import PartSpec
+            self.shared = SwiGLUMLP(PartSpec("swiglu_mlp", GatedMLPParams(
+                p.hidden_size, p.shared_intermediate_size, activation=p.shared_activation or p.activation,
+                limit=p.shared_limit or p.limit, slope=p.slope)), rt)
+        elif p.shared_intermediate_size > 0:
             from .spec import PartSpec
             self.shared = ActMLP(PartSpec("act_mlp", ActMLPParams(p.hidden_size, p.shared_intermediate_size,
                                                                   p.shared_activation or p.activation)), rt)
 
     def tensors(self) -> Dict[str, TensorSpec]:
         p = self.params
-        t = {"router": TensorSpec((p.num_experts, p.hidden_size))}
+        t = {"router": TensorSpec((self.outputs, p.hidden_size))}
         if p.router_bias:
-            t["router_bias"] = TensorSpec((p.num_experts,))
+            t["router_bias"] = TensorSpec((self.outputs,))
+        if p.choice_bias:
+            t["choice_bias"] = TensorSpec((self.outputs,))
         for e in range(p.num_experts):
             if p.gated:
                 t[f"gate{e}"] = TensorSpec((p.intermediate_size, p.hidden_size))
             t[f"up{e}"] = TensorSpec((p.intermediate_size, p.hidden_size))
             t[f"down{e}"] = TensorSpec((p.hidden_size, p.intermediate_size))
         if self.shared is not None:
+            if p.gated:
+                t["shared_gate"] = TensorSpec((p.shared_intermediate_size, p.hidden_size))
             t["shared_up"] = TensorSpec((p.shared_intermediate_size, p.hidden_size))
             t["shared_down"] = TensorSpec((p.hidden_size, p.shared_intermediate_size))
         return t
@@ -133,9 +161,12 @@ class RoutedExperts(FeedForward):
 
         self.w_up = stacked("up_all", "up")            # [experts * ff, hidden] (gated: [experts * 2 ff, hidden])
         self.b_router = tensors["router_bias"].float().contiguous() if p.router_bias else None
+        self.b_choice = tensors["choice_bias"].float().contiguous() if p.choice_bias else None
         self.w_down = stacked("down_all", "down")      # [experts * hidden, ff]
         self.w_router = tensors["router"]
-        if self.shared is not None:
+        if self.shared is not None and p.gated:
+            self.shared.load({"gate": tensors["shared_gate"], "up": tensors["shared_up"], "down": tensors["shared_down"]})
+        elif self.shared is not None:
             self.shared.load({"up": tensors["shared_up"], "down": tensors["shared_down"]})
 
     def nbytes(self) -> int:
@@ -148,8 +179,8 @@ class RoutedExperts(FeedForward):
         ws = rt.workspace
         pairs = T * p.top
         max_pairs = rt.max_tokens * p.top
-        max_tiles = kernels.moe_max_tiles(pairs, p.num_experts)
-        cap_tiles = kernels.moe_max_tiles(max_pairs, p.num_experts)
+        max_tiles = kernels.moe_max_tiles(pairs, max(p.num_experts, 1))
+        cap_tiles = kernels.moe_max_tiles(max_pairs, max(p.num_experts, 1))
         choice = ws.get("moe.choice", (max_pairs,), torch.int32)
         weight = ws.get("moe.weight", (max_pairs,), torch.float32)
         order = ws.get("moe.order", (max_pairs,), torch.int32)
@@ -158,11 +189,13 @@ class RoutedExperts(FeedForward):
         tile_rows = ws.get("moe.tile_rows", (cap_tiles,), torch.int32)
         meta = ws.get("moe.meta", (4,), torch.int32)
         # the router's logits as a matrix product with float32 sums and a float32 result, then the choice
-        logits = ws.get("moe.logits", (rt.max_tokens, p.num_experts), torch.float32)[:T]
+        logits = ws.get("moe.logits", (rt.max_tokens, self.outputs), torch.float32)[:T]
         linear(x, self.w_router, logits)
         kernels.moe_route(logits, None, choice, weight, T, p.groups, p.group_keep, p.group_top, p.top,
-                          softmax=p.score == "softmax", renorm=p.renormalize, bias=self.b_router)
-        kernels.moe_group(choice, pairs, p.num_experts, order, tile_expert, tile_begin, tile_rows, meta)
+                          softmax=p.score == "softmax", renorm=p.renormalize, bias=self.b_router,
+                          choice_bias=self.b_choice, weight_scale=p.weight_scale, renorm_floor=p.renorm_floor)
+        kernels.moe_group(choice, pairs, self.outputs, order, tile_expert, tile_begin, tile_rows, meta,
+                          tiled=p.num_experts)
         op_mark(ctx, "route", self.w_router, T)
         if x.dtype != self.w_up.dtype:
             raise kernels.KernelError("routed_experts: expert weights must have the activation type")
@@ -172,7 +205,7 @@ class RoutedExperts(FeedForward):
         if p.gated:
             gu = ws.get("moe.gate_up", (max_pairs, 2 * p.intermediate_size), rt.dtype)[:pairs]
             kernels.moe_gemm(x, p.top, self.w_up, gu, *lists)
-            kernels.gated_act(gu, act, self.act)
+            kernels.gated_act(gu, act, self.act, p.limit, p.slope)
         else:
             kernels.moe_gemm(x, p.top, self.w_up, act, *lists, act=self.act)
         kernels.moe_gemm(act, 1, self.w_down, y, *lists)
@@ -181,8 +214,13 @@ class RoutedExperts(FeedForward):
         op_mark(ctx, "experts", nbytes=float(min(pairs, p.num_experts) * mats * p.intermediate_size * p.hidden_size * elem
                                              + pairs * (mats * p.intermediate_size + 2 * p.hidden_size) * elem),
                 flops=2.0 * mats * pairs * p.intermediate_size * p.hidden_size)
-        shared = self.shared.run(x, ctx, "moe.shared") if self.shared is not None else None
+        shared = None
+        if self.shared is not None:
+            shared = self.shared.run(x, ctx, "moe.shared")
         out = ws.get("ffn.out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
-        kernels.moe_combine(y, weight, shared, out, T, p.top)
+        if p.identity > 0:
+            kernels.moe_combine(y, weight, shared, out, T, p.top, choice=choice, real_experts=p.num_experts, x=x)
+        else:
+            kernels.moe_combine(y, weight, shared, out, T, p.top)
         op_mark(ctx, "combine", nbytes=float((pairs + 2 * T) * p.hidden_size * elem))
         return out

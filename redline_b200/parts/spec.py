@@ -53,10 +53,14 @@ class LayerCall:
     cache_of     None: this call owns a cache of its own and writes it;
                  an int: index of an earlier call whose cache this call reads
                  (it then writes none)
+    add_embedding  the embedding output (the stream as it was before the first layer) is added to the stream
+                 right before this call: designs that run some layers several times feed the input in again
+                 before every repetition
     """
 
     layer: int
     cache_of: Optional[int] = None
+    add_embedding: bool = False
 
 
 @dataclass(frozen=True)

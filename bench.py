@@ -502,9 +502,9 @@ def main() -> int:
     ap.add_argument("--profile-batch", type=int, default=BATCH)
     ap.add_argument("--profile-prompt", type=int, default=0, help="with --profile-step: prompt length (default: context - 96)")
     ap.add_argument("--profile-eager", action="store_true", help="with --profile-step: no CUDA graph")
-    ap.add_argument("--compare-design", default="", choices=["", "kapitar", "pufevik", "vizotar"],
+    ap.add_argument("--compare-design", default="", choices=["", "kapitar", "pufevik", "vizotar", "venezen"],
                     help="instead of the headline run: prefill and decode throughput of this architecture beside "
-                         "the closest one the package has (Llama; Pufevik for vizotar) at equal layer sizes, with the "
+                         "the closest one the package has (Llama; Pufevik for vizotar, Kapitar for venezen) at equal layer sizes, with the "
                          "per-op roofline fractions of both")
     ap.add_argument("--compare-sizes", default="s,m", help="with --compare-design: which of its sizes (s, m)")
     ap.add_argument("--compare-no-ops", action="store_true", help="with --compare-design: no per-op tables")

@@ -21,6 +21,14 @@ Pufevik, the closest architecture the package has (the same pair without convolu
 attention where Vizotar has the delta rule, dense feed-forwards), at the same width, heads, head sizes,
 window, memory sizes and feed-forward width; the routed layers' chosen experts together are as wide as the
 dense feed-forward.
+
+The Venezen model has four layers: attention over a cached latent with a dense gated feed-forward, windowed
+attention whose keys are its values with routed experts (identity experts among the router's outputs, a shared
+expert), the latent attention with routed experts, the windowed attention with a dense feed-forward.  Beside
+it stands Kapitar, the closest architecture the package has (layer norms, attention through the same kernels
+over the same window with two score maps of half the key size, routed experts with a shared one; linear
+attention where Venezen attends over latents), at the same width, heads, kv heads, window and expert count;
+Venezen's gated feed-forwards have three matrices for Kapitar's two and are two thirds as wide.
 """
 
 from __future__ import annotations
@@ -50,6 +58,14 @@ VIZOTAR_SIZES: Dict[str, Dict[str, int]] = {
     "m": dict(width=2048, heads=16, kv_heads=4, dim=128, vdim=128, ff=5632, mem_heads=16, mem_dim=64, mem_vdim=128,
               delta_heads=16, delta_qk_heads=8, delta_dim=128, delta_vdim=128, rank=128, experts=32, top=4, expert_ff=1408,
               streams=4, taps=4, vocab=32000),
+}
+VENEZEN_SIZES: Dict[str, Dict[str, int]] = {
+    # SIZES' keys for the Kapitar model beside it, plus the latent attention's sizes (a cached row of kv_rank + rot_dim
+    # entries), the gated feed-forwards' widths (two thirds of Kapitar's ungated ones) and the identity experts
+    "s": dict(SIZES["s"], lat_dim=64, rot_dim=32, lat_vdim=64, kv_rank=192, gated_ff=2816, gated_expert_ff=384,
+              gated_shared_ff=768, identity=2),
+    "m": dict(SIZES["m"], lat_dim=64, rot_dim=32, lat_vdim=64, kv_rank=192, gated_ff=5632, gated_expert_ff=704,
+              gated_shared_ff=1408, identity=4),
 }
 WINDOW, KEEP_FIRST = 1024, 4
 PROMPT = 2048
@@ -110,10 +126,26 @@ def vizotar_config(s: Dict[str, int]) -> Dict[str, Any]:
                        {"type": "parallel", "mixer": pair, "mlp": moe}, {"type": "channel_delta", "mixer": delta, "mlp": dense}]}
 
 
+def venezen_config(s: Dict[str, int]) -> Dict[str, Any]:
+    latent = {"heads": s["heads"], "dim": s["lat_dim"], "rot_dim": s["rot_dim"], "vdim": s["lat_vdim"], "kv_rank": s["kv_rank"],
+              "scale": (s["lat_dim"] + s["rot_dim"]) ** -0.5, "rot": {"base": 500000.0, "dims": s["rot_dim"]}}
+    key = 2 * s["dim"]                                     # Kapitar's two maps together
+    windowed = {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": key, "vdim": key, "scale": key ** -0.5,
+                "mask": {"size": WINDOW}}
+    dense = {"kind": "dense", "ff": s["gated_ff"]}
+    moe = {"kind": "moe", "expert": {"ff": s["gated_expert_ff"], "limit": 7.0}, "shared": {"ff": s["gated_shared_ff"], "limit": 7.0},
+           "router": {"experts": s["experts"], "identity": s["identity"], "top": s["top"], "scale": 2.5}}
+    return {"architecture": "Venezen", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0},
+            "layers": [{"type": "latent_attention", "mixer": latent, "mlp": dense}, {"type": "attention", "mixer": windowed, "mlp": moe},
+                       {"type": "latent_attention", "mixer": latent, "mlp": moe}, {"type": "attention", "mixer": windowed, "mlp": dense}]}
+
+
 # design -> (its sizes, its configuration, the architecture beside it, that one's configuration at the same sizes)
 DESIGNS = {"kapitar": (SIZES, kapitar_config, "llama", llama_config),
            "pufevik": (PUFEVIK_SIZES, pufevik_config, "llama", llama_beside_pufevik),
-           "vizotar": (VIZOTAR_SIZES, vizotar_config, "pufevik", pufevik_config)}
+           "vizotar": (VIZOTAR_SIZES, vizotar_config, "pufevik", pufevik_config),
+           "venezen": (VENEZEN_SIZES, venezen_config, "kapitar", kapitar_config)}
 
 
 def _prefill(model: str, tokens: int, reps: int, warmup: int) -> float:

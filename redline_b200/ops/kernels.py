@@ -1270,7 +1270,12 @@ def build_all(head_dims=(64, 128), maps_dims=((64, 128, 2), (128, 128, 1)), line
     ]
     for d in head_dims:
         built.append(build.compile_module(f"attention_d{d}", "attention.cu", {"RL_HEAD_DIM": d}, verbose=verbose))
-    for d, v, m in maps_dims:
+    for d, v, m, *stride in maps_dims:         # (key size, value size, maps[, length of a value row if longer])
+        if stride and stride[0] not in (0, v):
+            built.append(build.compile_module(f"attention_maps_d{d}_v{v}_m{m}_s{stride[0]}", "attention_maps.cu",
+                                              {"RL_QK_DIM": d, "RL_V_DIM": v, "RL_MAPS": m, "RL_V_STRIDE": stride[0]},
+                                              verbose=verbose))
+            continue
         built.append(build.compile_module(f"attention_maps_d{d}_v{v}_m{m}", "attention_maps.cu",
                                           {"RL_QK_DIM": d, "RL_V_DIM": v, "RL_MAPS": m}, verbose=verbose))
     for d in linear_dims:

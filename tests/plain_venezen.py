@@ -71,13 +71,15 @@ def rotate_halves(x: torch.Tensor, base: float, dims: int, positions: Sequence[i
     with entry i + dims/2; the rest unchanged."""
     half = dims // 2
     out = x.clone()
-    for t, p in enumerate(positions):
-        for i in range(half):
-            a = p * base ** (-2.0 * i / dims)
-            c, s = math.cos(a), math.sin(a)
-            u, v = x[t, ..., i], x[t, ..., i + half]
-            out[t, ..., i] = u * c - v * s
-            out[t, ..., i + half] = v * c + u * s
+    if half == 0:
+        return out
+    freq = torch.tensor([base ** (-2.0 * i / dims) for i in range(half)], dtype=torch.float64)
+    ang = torch.tensor(list(positions), dtype=torch.float64)[:, None] * freq[None, :]
+    shape = [x.shape[0]] + [1] * (x.dim() - 2) + [half]
+    c, s = torch.cos(ang).to(x.dtype).view(shape), torch.sin(ang).to(x.dtype).view(shape)
+    u, v = x[..., :half], x[..., half:dims]
+    out[..., :half] = u * c - v * s
+    out[..., half:dims] = v * c + u * s
     return out
 
 
@@ -122,7 +124,7 @@ def biased_window_weights(s: torch.Tensor, slope: float, size: int) -> torch.Ten
     i = torch.arange(T).view(T, 1)
     j = torch.arange(T).view(1, T)
     dist = (i - j).to(F64)
-    seen = (dist >= 0) & (dist < size)
+    seen = (dist >= 0) & ((dist < size) if size > 0 else (dist >= 0))          # size 0: no window
     s = (s - slope * dist).masked_fill(~seen, -math.inf)
     mx = torch.clamp(s.max(-1, keepdim=True).values, min=0.0)          # the added one is exp(0)
     e = torch.exp(s - mx)
@@ -139,7 +141,7 @@ def window_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, m: dic
     out = torch.zeros(T, H, d, dtype=F64)
     for hd in range(H):
         g = hd // (H // G)
-        a = biased_window_weights(q[:, hd] @ k[:, g].T * m["scale"], slopes[hd], m["mask"]["size"])
+        a = biased_window_weights(q[:, hd] @ k[:, g].T * m["scale"], slopes[hd], (m.get("mask") or {}).get("size", 0))
         out[:, hd] = a @ k[:, g]
     return stored(stored(out.reshape(T, H * d)) @ w[p + "o"].T)
 
@@ -170,15 +172,16 @@ def routed_ff(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, f: dict) -> t
     r = f["router"]
     pick, weight = route(h, w, p, f)
     out = torch.zeros_like(h)
-    for t in range(h.shape[0]):
-        for k in range(r["top"]):
-            e = int(pick[t, k])
-            if e >= r["experts"]:
-                y = h[t]
-            else:
-                y = clamped_expert(h[t:t + 1], w[f"{p}e{e}.gate"], w[f"{p}e{e}.up"], w[f"{p}e{e}.down"],
-                                   f["expert"]["limit"])[0]
-            out[t] += weight[t, k] * y
+    for e in range(r["experts"] + r["identity"]):
+        hit = pick == e                                   # [T, top]: which tokens chose output e, and where
+        rows = hit.any(-1).nonzero().flatten()
+        if rows.numel() == 0:
+            continue
+        if e >= r["experts"]:
+            y = h[rows]
+        else:
+            y = clamped_expert(h[rows], w[f"{p}e{e}.gate"], w[f"{p}e{e}.up"], w[f"{p}e{e}.down"], f["expert"]["limit"])
+        out[rows] += (weight[rows] * hit[rows]).sum(-1, keepdim=True) * y
     if f.get("shared") is not None:
         out = out + clamped_expert(h, w[p + "shared.gate"], w[p + "shared.up"], w[p + "shared.down"], f["shared"]["limit"])
     return stored(out)

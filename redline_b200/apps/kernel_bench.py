@@ -6,6 +6,8 @@ package, if present).
     python -m redline_b200.apps.kernel_bench skinny --rows 8 --n 3072 --k 2048 [--norm] [--epilogue swiglu]
     python -m redline_b200.apps.kernel_bench attn_prefill --tokens 2048
     python -m redline_b200.apps.kernel_bench gemm_tc --rows 2048 --n 8192 --k 2048 --epilogue swiglu [--library]
+    python -m redline_b200.apps.kernel_bench head_linear --tokens 2048 --heads 16 --n 192 --k 64 [--impl 1]
+    python -m redline_b200.apps.kernel_bench latent_attn --tokens 2048 --heads 16 --rank 192 --rot 32 [--impl 1]
 
 Each kernel runs over several distinct copies of its large operands (more than the
 L2 holds), captured in a CUDA graph so that launch overhead of the host is not
@@ -223,10 +225,62 @@ def bench_attn_prefill(args) -> None:
                       "frac_of_measured_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 4)}))
 
 
+def bench_head_linear(args) -> None:
+    """The per-head products around an attention over latents: y[t, h] = W_h x[t, h]."""
+    dev = "cuda"
+    T, H, N, K = args.tokens, args.heads, args.n, args.k
+    copies = max(2, min(args.copies, int(2e9 // (T * H * (N + K) * 2))))
+    xs = [torch.randn(T, H * K, device=dev).to(torch.bfloat16) for _ in range(copies)]
+    ys = [torch.empty(T, H * N, device=dev, dtype=torch.bfloat16) for _ in range(copies)]
+    w = (torch.randn(H, N, K, device=dev) / math.sqrt(K)).to(torch.bfloat16)
+
+    def fn(i):
+        kernels.head_linear(xs[i % copies], 0, K, w, ys[i % copies], 0, N, impl=args.impl)
+
+    us = graph_time_us(fn, copies, use_graph=not args.no_graph)
+    nbytes, flops = T * H * (N + K) * 2.0 + w.numel() * 2.0, 2.0 * T * H * N * K
+    pk = peaks()
+    print(json.dumps({"kernel": "head_linear", "impl": args.impl, "tokens": T, "heads": H, "n": N, "k": K, "us": round(us, 2),
+                      "GB/s": round(nbytes / us / 1e3, 1), "TFLOP/s": round(flops / us / 1e6, 1),
+                      "frac_of_measured_hbm": round(nbytes / us / 1e3 / pk["hbm_gbs"], 3),
+                      "frac_of_measured_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 4), "copies": copies}))
+
+
+def bench_latent_attn(args) -> None:
+    """A prompt portion's attention over cached latents: every head's query of rank + rot entries against the one
+    cached row per token, whose first ``rank`` entries are the value."""
+    dev = "cuda"
+    T, H, rank, rot, ps = args.tokens, args.heads, args.rank, args.rot, args.page_size
+    D = rank + rot
+    npages = (T + ps - 1) // ps + 1
+    k = torch.randn(npages, 1, ps, D, device=dev).to(torch.bfloat16)
+    bt = (torch.arange(npages - 1, dtype=torch.int32) + 1).view(1, -1).to(dev)
+    q = torch.randn(T, H * D, device=dev).to(torch.bfloat16)
+    pos = torch.arange(T, dtype=torch.int32, device=dev)
+    rows = kernels.PREFILL_TILE_ROWS
+    nt = (T + rows - 1) // rows
+    tile_seq = torch.zeros(nt, dtype=torch.int32, device=dev)
+    tile_tok = (torch.arange(nt, dtype=torch.int32) * rows).to(dev)
+    tile_rows = torch.tensor([min(rows, T - i * rows) for i in range(nt)], dtype=torch.int32, device=dev)
+    out = torch.empty(T, H * rank, device=dev, dtype=torch.bfloat16)
+
+    def fn(i):
+        kernels.maps_attn_prefill(q, H * D, k, k, bt, tile_seq, tile_tok, tile_rows, pos, out, nt, rows, H, 1, D, rank, 1, ps,
+                                  0, 0, 1.0 / math.sqrt(D), 0.0, 0.0, 1.0, 1e-6, False, impl=args.impl,
+                                  v_stride=D if rot > 0 else 0)
+
+    us = graph_time_us(fn, 8 if T <= 4096 else 2, replays=5, use_graph=not args.no_graph)
+    flops = H * 2.0 * (D + rank) * (T * (T + 1) / 2.0)
+    pk = peaks()
+    print(json.dumps({"kernel": "latent_attn_prefill", "impl": args.impl, "tokens": T, "heads": H, "rank": rank, "rot": rot,
+                      "us": round(us, 1), "TFLOP/s": round(flops / us / 1e6, 1),
+                      "frac_of_measured_bf16": round(flops / us / 1e6 / pk["bf16_tflops"], 4)}))
+
+
 def main() -> int:
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     sub = ap.add_subparsers(dest="kernel", required=True)
-    for name in ("attn_decode", "attn_prefill", "skinny", "gemm_tc", "gemm_mid"):
+    for name in ("attn_decode", "attn_prefill", "skinny", "gemm_tc", "gemm_mid", "head_linear", "latent_attn"):
         p = sub.add_parser(name)
         p.add_argument("--heads", type=int, default=32)
         p.add_argument("--kv-heads", type=int, default=8)
@@ -239,6 +293,13 @@ def main() -> int:
             p.add_argument("--ctx", type=int, default=4096)
             p.add_argument("--impl", type=int, default=0,
                            help="0 auto, 1 CUDA cores, 2 one-partition mma.sync kernel, 3 streaming kernel")
+        if name in ("head_linear", "latent_attn"):
+            p.add_argument("--tokens", type=int, default=2048)
+            p.add_argument("--impl", type=int, default=0, help="0 auto (tensor cores where they apply), 1 CUDA cores")
+            p.add_argument("--n", type=int, default=192, help="head_linear: outputs of a head")
+            p.add_argument("--k", type=int, default=64, help="head_linear: inputs of a head")
+            p.add_argument("--rank", type=int, default=192, help="latent_attn: size of the cached latent")
+            p.add_argument("--rot", type=int, default=32, help="latent_attn: size of the rotated key part")
         if name == "attn_prefill":
             p.add_argument("--tokens", type=int, default=2048)
             p.add_argument("--impl", type=int, default=0, help="0 auto, 1 CUDA cores, 2 mma.sync kernel, 3 tcgen05 kernel")
@@ -272,7 +333,8 @@ def main() -> int:
         print("kernel_bench needs a CUDA device", file=sys.stderr)
         return 1
     {"attn_decode": bench_attn_decode, "attn_prefill": bench_attn_prefill, "skinny": bench_skinny,
-     "gemm_tc": bench_gemm_tc, "gemm_mid": bench_gemm_mid}[args.kernel](args)
+     "gemm_tc": bench_gemm_tc, "gemm_mid": bench_gemm_mid, "head_linear": bench_head_linear,
+     "latent_attn": bench_latent_attn}[args.kernel](args)
     return 0
 
 

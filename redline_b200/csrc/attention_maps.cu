@@ -43,7 +43,9 @@ namespace rl {
 constexpr int kD = RL_QK_DIM, kDV = RL_V_DIM, kM = RL_MAPS, kVS = RL_V_STRIDE;
 static_assert(kVS >= kDV, "a value row holds the value");
 static_assert(kM == 1 || kM == 2, "one or two score maps");
-static_assert(kD >= 1 && kD <= 256 && kDV >= 1 && kDV <= 256, "sizes out of range");
+// (up to 256 entries every kernel applies; longer rows, up to 576, go through the CUDA-core kernels only: what
+// the single-token kernel keeps in static shared memory and the portion kernel in dynamic shared memory still fits)
+static_assert(kD >= 1 && kD <= 576 && kDV >= 1 && kDV <= 512, "sizes out of range");
 constexpr int kVQ = (kDV + 3) / 4;             // value columns of one of the four threads that share a query row
 constexpr int kPart = 128;
 constexpr int kThreads = 128;
@@ -513,7 +515,7 @@ maps_prefill_kernel(const MapsPrefillArgs<T> a) {
 // into the same float32 accumulator), which keeps 16 bits of mantissa.  Both maps run in turn over the
 // visible tiles; the first map's result waits in shared memory; combination, unit norm and the bfloat16
 // store are the epilogue.
-#if (RL_QK_DIM % 16 == 0) && (RL_V_DIM % 16 == 0) && (RL_V_STRIDE % 8 == 0)
+#if (RL_QK_DIM % 16 == 0) && (RL_V_DIM % 16 == 0) && (RL_V_STRIDE % 8 == 0) && (RL_QK_DIM <= 256) && (RL_V_DIM <= 256)
 #define RL_MAPS_HAVE_MMA 1
 constexpr int kTQ = 64, kTK = 64;
 constexpr int kLDK = kD + 8, kLDV = kDV + 8;      // shared-memory row lengths in elements

@@ -164,6 +164,7 @@ head_linear_mma_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, b
   float acc[kHmCols / 8][4];
 #pragma unroll
   for (int nt = 0; nt < kHmCols / 8; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
+#pragma unroll 4
   for (int k0 = 0; k0 < a.k; k0 += 16) {
     uint32_t af[4];
     af[0] = *reinterpret_cast<const uint32_t*>(x0 + k0);

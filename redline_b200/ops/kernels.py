@@ -718,12 +718,15 @@ def head_prep(x: torch.Tensor, positions: torch.Tensor, tokens: int, q_col: int,
 
 # ------------------------------------ attention with score maps, a capped score and kept first tokens
 
+MAPS_MAX_DIM, MAPS_MAX_VDIM = 576, 512      # (the tensor-core kernel takes sizes up to 256; longer rows run on CUDA cores)
+
+
 def _maps(dim: int, vdim: int, maps: int, v_stride: int = 0) -> ctypes.CDLL:
     """``v_stride``: the length of a row of the value cache when it is longer than a value (a mixer whose
     values are the leading entries of its keys hands the key cache in as the value cache); 0: ``vdim``."""
-    if not (1 <= dim <= 256 and 1 <= vdim <= 256 and maps in (1, 2)):
-        raise KernelError(f"attention_maps takes key and value sizes up to 256 and one or two maps; "
-                          f"got {dim}, {vdim}, {maps}")
+    if not (1 <= dim <= MAPS_MAX_DIM and 1 <= vdim <= MAPS_MAX_VDIM and maps in (1, 2)):
+        raise KernelError(f"attention_maps takes key sizes up to {MAPS_MAX_DIM}, value sizes up to {MAPS_MAX_VDIM} and one "
+                          f"or two maps; got {dim}, {vdim}, {maps}")
     if v_stride in (0, vdim):
         return _lib(f"attention_maps_d{dim}_v{vdim}_m{maps}", "attention_maps.cu",
                     {"RL_QK_DIM": dim, "RL_V_DIM": vdim, "RL_MAPS": maps})

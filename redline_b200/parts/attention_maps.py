@@ -81,8 +81,9 @@ class MapsAttention(Mixer):
             raise ValueError(f"num_heads {p.num_heads} is no multiple of num_kv_heads {p.num_kv_heads}")
         if p.maps not in (1, 2):
             raise ValueError(f"attention with {p.maps} score maps is not supported (1 or 2)")
-        if not (1 <= p.dim <= 256 and 1 <= p.vdim <= 256):
-            raise ValueError(f"attention_maps kernels take key and value sizes up to 256; got dim={p.dim}, vdim={p.vdim}")
+        if not (1 <= p.dim <= kernels.MAPS_MAX_DIM and 1 <= p.vdim <= kernels.MAPS_MAX_VDIM):
+            raise ValueError(f"attention_maps kernels take key sizes up to {kernels.MAPS_MAX_DIM} and value sizes up to "
+                             f"{kernels.MAPS_MAX_VDIM}; got dim={p.dim}, vdim={p.vdim}")
         self.position = build_part("position", p.position, rt) if p.position is not None else None
         self.rotary = None           # (cos, sin) of an encoding whose pairs the head kernel rotates
         self.halves = False          # ... entry i with entry i + half instead of its neighbour

@@ -49,9 +49,9 @@ class LatentAttention(Mixer):
         self.key_size = p.kv_rank + p.rot_dim          # a cached row, and a head's query for the kernels
         if min(p.num_heads, p.dim, p.vdim, p.kv_rank) <= 0 or p.rot_dim < 0:
             raise ValueError("latent_attention: heads, dim, vdim and kv_rank must be positive")
-        if self.key_size > 256:
+        if self.key_size > kernels.MAPS_MAX_DIM or p.kv_rank > kernels.MAPS_MAX_VDIM:
             raise ValueError(f"latent_attention: kv_rank + rot_dim is {self.key_size}; the attention kernels take "
-                             "rows of up to 256 entries")
+                             f"rows of up to {kernels.MAPS_MAX_DIM} entries of which {kernels.MAPS_MAX_VDIM} are the latent")
         self.cos = self.sin = None
         self.rot_dims = 0
         if p.rot_dim > 0:

@@ -471,3 +471,25 @@ def test_trace_run_program(dtype, models, tmp_path):
     check(np.concatenate([f[0], f[1][:1], f[3][:1]]), cfg, w, a, dtype, rows=[0, 39, 41, 69])
     check(f[1][1:], cfg, w, b, dtype, rows=[44])
     check(f[3][1:], cfg, w, b[:2], dtype, rows=[1, 0])
+
+
+def test_command_line_with_random_weights(tmp_path):
+    """`bin/redline_generate --random-weights`: the framework writes a seeded Venezen model from a config.json,
+    generates greedily, and the plain implementation, reading that folder, agrees with every token."""
+    cfg_path = tmp_path / "config.json"
+    cfg_path.write_text(json.dumps(C.MIX))
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    r = subprocess.run([sys.executable, os.path.join(root, "bin", "redline_generate"), "--random-weights", str(cfg_path),
+                        "--weights-seed", "5", "--model", str(tmp_path / "rand"), "--dtype", "float32", "--prompt-ids",
+                        "1,2,3,50,9", "--prompt-ids", "7", "--max-new-tokens", "8", "--ignore-eos", "--max-seq-len", "64",
+                        "--kv-cache-tokens", "256", "--max-seqs", "2"], capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0, r.stderr[-2000:]
+    lines = [json.loads(x) for x in r.stdout.splitlines() if x.startswith("{")]
+    assert [x["id"] for x in lines] == [0, 1] and all(len(x["output_ids"]) == 8 for x in lines)
+    cfg, w = P.read_model_dir(str(tmp_path / "rand"))
+    for prompt, line in zip(([1, 2, 3, 50, 9], [7]), lines):
+        seq = prompt + line["output_ids"]
+        ref = oracle(cfg, w, seq[:-1])
+        for i, tok in enumerate(line["output_ids"]):
+            row = ref[len(prompt) - 1 + i]
+            assert row[tok] >= row.max() - 1e-3, (i, tok, int(row.argmax()))

@@ -545,7 +545,11 @@ __device__ __forceinline__ float tanh_fast(float x) {
 // 16 heads, window 1,024: two stages and two CTAs 0.42 ms, one stage and three CTAs 0.32 ms).
 constexpr int kStages = 1;
 
-__global__ void __launch_bounds__(128, 3)
+// (three CTAs to an SM cap a thread at 168 registers, which the query fragments and the output accumulators of
+//  long rows do not fit: those sizes take two CTAs and up to 255 registers instead of spilling)
+constexpr int kMmaCtas = (kD + kDV > 288) ? 2 : 3;
+
+__global__ void __launch_bounds__(128, kMmaCtas)
 maps_prefill_mma_kernel(const MapsPrefillArgs<bf16> a) {
   pdl_launch();
   pdl_wait();

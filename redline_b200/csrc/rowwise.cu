@@ -254,18 +254,21 @@ __global__ void gated_rmsnorm_kernel(const float* __restrict__ o, const TA* __re
 // mode ACT_CLAMPED_SWISH: g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(slope g) (u + 1).
 template <typename TA>
 __global__ void gated_act_kernel(const TA* __restrict__ gu, int ld, TA* __restrict__ out, int inter, int mode,
-                                 float limit, float slope) {
+                                 float limit, float slope, const float* __restrict__ bias) {
   pdl_launch();
   pdl_wait();
   const TA* g = gu + static_cast<size_t>(blockIdx.y) * ld;
   TA* o = out + static_cast<size_t>(blockIdx.y) * inter;
   for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < inter; c += gridDim.x * blockDim.x) {
+    // (a bias [gate | up] of the product before is added on the way in)
+    const float gate = to_float(g[c]) + (bias != nullptr ? bias[c] : 0.f);
+    const float up = to_float(g[inter + c]) + (bias != nullptr ? bias[inter + c] : 0.f);
     if (mode == ACT_CLAMPED_SWISH) {
-      const float z = fminf(to_float(g[c]), limit);
-      const float u = fminf(fmaxf(to_float(g[inter + c]), -limit), limit);
+      const float z = fminf(gate, limit);
+      const float u = fminf(fmaxf(up, -limit), limit);
       o[c] = from_float<TA>(z / (1.f + expf(-slope * z)) * (u + 1.f));
     } else {
-      o[c] = from_float<TA>(activate(to_float(g[c]), mode) * to_float(g[inter + c]));
+      o[c] = from_float<TA>(activate(gate, mode) * up);
     }
   }
 }
@@ -527,16 +530,16 @@ int rl_gated_rmsnorm(const float* o, const void* gate, int ld_gate, const void* 
 }
 
 int rl_gated_act(const void* gu, int ld, void* out, int act_dtype, int rows, int inter, int mode, float limit,
-                 float slope, cudaStream_t stream) {
+                 float slope, const float* bias, cudaStream_t stream) {
   if (rows <= 0 || inter <= 0) return 0;
   const int th = 256;
   dim3 grid(min((inter + th - 1) / th, 64), rows);
   if (act_dtype == RL_F32)
     launch_kernel(gated_act_kernel<float>, grid, dim3(th), 0, stream, static_cast<const float*>(gu), ld,
-                  static_cast<float*>(out), inter, mode, limit, slope);
+                  static_cast<float*>(out), inter, mode, limit, slope, bias);
   else
     launch_kernel(gated_act_kernel<bf16>, grid, dim3(th), 0, stream, static_cast<const bf16*>(gu), ld,
-                  static_cast<bf16*>(out), inter, mode, limit, slope);
+                  static_cast<bf16*>(out), inter, mode, limit, slope, bias);
   RL_LAUNCH_END();
 }
 

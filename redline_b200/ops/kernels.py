@@ -650,16 +650,21 @@ def gated_rmsnorm(o: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out
              rows if rows is not None else o.shape[0], o.shape[1], float(eps), _stream()), "gated_rmsnorm")
 
 
-def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: int, limit: float = 0.0, slope: float = 1.0) -> None:
+def gated_act(gate_up: torch.Tensor, out: torch.Tensor, act: int, limit: float = 0.0, slope: float = 1.0,
+              bias: Optional[torch.Tensor] = None) -> None:
     """out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i], I = out.shape[1].  ``ACT_CLAMPED_SWISH``: with
-    g = min(gate, limit) and u = clamp(up, -limit, limit), out = g * sigmoid(slope * g) * (u + 1)."""
-    _need_cuda(gate_up, out)
+    g = min(gate, limit) and u = clamp(up, -limit, limit), out = g * sigmoid(slope * g) * (u + 1).  ``bias``
+    (float32 [2 I], gate's then up's) is added to gate and up on the way in."""
+    _need_cuda(gate_up, out, bias)
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != gate_up.shape[1] or not bias.is_contiguous()):
+        raise KernelError("gated_act: the bias is contiguous float32 [gate | up]")
     if gate_up.stride(1) != 1 or not out.is_contiguous() or gate_up.dtype != out.dtype \
             or gate_up.shape[1] != 2 * out.shape[1]:
         raise KernelError("gated_act: [gate | up] rows of the output's type and twice its width")
-    f = _fn(_rw(), "rl_gated_act", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p])
+    f = _fn(_rw(), "rl_gated_act", [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_float, c_float, c_void_p,
+                                     c_void_p])
     _check(f(_ptr(gate_up), gate_up.stride(0), _ptr(out), _code(out.dtype), out.shape[0], out.shape[1], act,
-             float(limit), float(slope), _stream()), "gated_act")
+             float(limit), float(slope), _ptr(bias), _stream()), "gated_act")
 
 
 HEAD_NORM_NONE, HEAD_NORM_EACH, HEAD_NORM_WHOLE = 0, 1, 2

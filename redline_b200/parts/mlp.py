@@ -99,14 +99,13 @@ class SwiGLUMLP(FeedForward):
         else:
             gu = ws.get(name + ".gate_up", (rt.max_tokens, 2 * p.intermediate_size), rt.dtype)[:T]
             linear(x, self.w_gate_up, gu)
-            if self.b_gate_up is not None:
-                kernels.add_bias(gu, self.b_gate_up)
-            if self.silu:
+            # (biases of gate and up are added by the activation kernel on its way in)
+            if self.silu and self.b_gate_up is None:
                 kernels.swiglu(gu, act)
             elif self.clamped:
-                kernels.gated_act(gu, act, kernels.ACT_CLAMPED_SWISH, p.limit, p.slope)
+                kernels.gated_act(gu, act, kernels.ACT_CLAMPED_SWISH, p.limit, p.slope, bias=self.b_gate_up)
             else:
-                kernels.gated_act(gu, act, kernels.ACTIVATIONS[self.params.activation])
+                kernels.gated_act(gu, act, kernels.ACTIVATIONS[self.params.activation], bias=self.b_gate_up)
         op_mark(ctx, "gate_up+swiglu" if self.silu else "gate_up+act", self.w_gate_up, T)
         out = ws.get(name + ".out", (rt.max_tokens, p.hidden_size), rt.dtype)[:T]
         linear(act, self.w_down, out)

@@ -22,7 +22,7 @@
 // cache in as the value cache with VS = D); out [tokens, out_stride] with head h at column h * DV.
 //
 // Scores, softmax, the combination of the maps and the norm are float32 for both element types.
-// Single tokens: one CTA per (128-key partition, kv head, item) over absolute partitions, so a row's
+// Single tokens: one CTA per (128-key partition, kv head and four of its query heads, item) over absolute partitions, so a row's
 // sums do not depend on what else is in the launch; a second kernel merges the partitions of a head's
 // maps, combines them and norms.  Prompt portions: both maps in turn over the visible key tiles,
 // combination and norm in the epilogue; in bfloat16 with sizes that are multiples of 16 on the tensor
@@ -126,14 +126,16 @@ maps_decode_kernel(const MapsDecodeArgs<T> a) {
   __shared__ float red[kThreads / 32][kRows][kDV];
   __shared__ float stat_m[kRows], stat_l[kRows];
 
-  const int part = blockIdx.x, kvh = blockIdx.y, item = blockIdx.z;
+  // blockIdx.y: (kv head, group of up to kRows of its query heads): the groups of a kv head run side by side
+  const int G = a.heads / a.kv_heads;
+  const int groups = (G + kRows - 1) / kRows;
+  const int part = blockIdx.x, kvh = blockIdx.y / groups, g0 = (blockIdx.y % groups) * kRows, item = blockIdx.z;
   const int4 info = a.items[item];
   const int tok = info.x, seq = info.y, ctx = info.z;
   const int me = ctx - 1;                                // the query's position
   const int base = part * kPart;
   const int j_hi = min(ctx, base + kPart);
   if (!range_visible(base, j_hi, me, a.mask)) return;
-  const int G = a.heads / a.kv_heads;
   const int lane8 = threadIdx.x % kLPK, slot = threadIdx.x / kLPK;
   const int warp = threadIdx.x >> 5;
   const int32_t* bt = a.block_table + static_cast<size_t>(seq) * a.max_blocks;
@@ -148,7 +150,7 @@ maps_decode_kernel(const MapsDecodeArgs<T> a) {
 
   for (int m = 0; m < kM; ++m) {
     const int khead = kvh * kM + m;
-    for (int g0 = 0; g0 < G; g0 += kRows) {
+    {
       const int ng = min(kRows, G - g0);
       __syncthreads();
       for (int i = threadIdx.x; i < kRows * kD; i += kThreads) {
@@ -861,7 +863,9 @@ int launch_maps_decode(const void* q, int q_stride, const void* kc, const void* 
   a.post_scale = post_scale;
   a.eps = eps;
   a.unit_norm = unit_norm;
-  cudaError_t e = launch_kernel(maps_decode_kernel<T>, dim3(max_parts, kv_heads, nitems), dim3(kThreads), 0, stream, a);
+  const int groups = (heads / kv_heads + kRows - 1) / kRows;
+  cudaError_t e = launch_kernel(maps_decode_kernel<T>, dim3(max_parts, kv_heads * groups, nitems), dim3(kThreads), 0, stream,
+                                a);
   if (e != cudaSuccess) return static_cast<int>(e);
   e = launch_kernel(maps_merge_kernel<T>, dim3(nitems, heads), dim3(kThreads), 0, stream, a);
   return static_cast<int>(e);
